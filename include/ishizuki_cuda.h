@@ -1,0 +1,164 @@
+/* C ABI of the B200 verify-matmul library (libishizuki_cuda.so).
+ *
+ * This is the boundary a host binding (Swift over a SwiftPM C target, or ctypes) links against.
+ * It replaces, for NVIDIA B200, the kernel layer the reference reaches through
+ * MLXFast.metalKernel: each entry point names the reference interface it stands in for, by the
+ * file's path inside the reference project.
+ *
+ * Conventions
+ *   - Every pointer named *_dev is a device pointer on the context's GPU; the caller owns every
+ *     buffer. The library keeps non-owning pointers to weights and owns only its tables and
+ *     scratch memory.
+ *   - Activations are fp16 row-major [M, K]; outputs are fp16 [M, N] with leading dimension
+ *     ldy (elements), or [N, M] with leading dimension ldy when ISHI_OUT_TRANSPOSED is set.
+ *     Accumulation is fp32.
+ *   - Calls are asynchronous on the given CUDA stream (a cudaStream_t passed as void*; NULL is
+ *     the default stream). Calls that share a context or a projection share its scratch memory
+ *     and must be ordered on one stream (or otherwise not overlap on the GPU).
+ *   - Every function returns an ishi_status and never aborts the process. Where the reference
+ *     returns nil ("this shape is declined, fall back"), this library returns
+ *     ISHI_E_UNSUPPORTED or ISHI_E_SHAPE: there is no CPU or library fallback behind it.
+ */
+#ifndef ISHIZUKI_CUDA_H
+#define ISHIZUKI_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int ishi_status;
+enum {
+  ISHI_OK = 0,
+  ISHI_E_INVALID = 1,     /* null or misaligned pointer, bad enum value */
+  ISHI_E_SHAPE = 2,       /* a shape guard of the reference failed (K % 256, rows out of range ...) */
+  ISHI_E_UNSUPPORTED = 3, /* a format or width this library has no kernel for */
+  ISHI_E_CUDA = 4,        /* a CUDA runtime call failed; see ishi_last_error */
+  ISHI_E_TIMEOUT = 5,     /* a bounded device-side wait gave up; outputs of that call are invalid */
+  ISHI_E_NOMEM = 6
+};
+
+/* GGML block types, numbered as in GGUF (Sources/IshizukiKit/Config/GGUFFile.swift:13-44). */
+enum { ISHI_GGML_Q4_K = 12, ISHI_GGML_Q6_K = 14, ISHI_GGML_IQ2_XS = 17 };
+
+enum { ISHI_KIND_AFFINE = 0, ISHI_KIND_GGML = 1 };
+enum { ISHI_DT_F16 = 0, ISHI_DT_BF16 = 1, ISHI_DT_F32 = 2 };
+
+/* Which kernel family a call uses. AUTO applies the per-projection row-count crossover. */
+enum { ISHI_ROUTE_AUTO = 0, ISHI_ROUTE_GEMV = 1, ISHI_ROUTE_MMA = 2 };
+
+enum { ISHI_OUT_TRANSPOSED = 1 };
+
+typedef struct ishi_ctx ishi_ctx;
+typedef struct ishi_projection ishi_projection;
+
+/* One projection's weight, as PackedLinear's initialisers receive it
+ * (Sources/IshizukiKit/Core/Hadamard.swift:51-86 for affine packs, :110-124 for GGUF blocks).
+ * n is the number of output rows held by THIS weight buffer: an N-shard passes its own rows. */
+typedef struct ishi_weight_desc {
+  int32_t kind;           /* ISHI_KIND_* */
+  int32_t ggml_type;      /* ISHI_GGML_* when kind == GGML */
+  int32_t bits;           /* affine: 2, 4 or 8 */
+  int32_t group_size;     /* affine: 32, 64 or 128 */
+  int32_t scale_dtype;    /* affine: ISHI_DT_* of scales and biases */
+  int32_t hadamard_block; /* 0, or the power-of-two block of the input rotation */
+  int64_t n;              /* output rows in this buffer */
+  int64_t k;              /* input width */
+  const void *weight_dev; /* GGUF: raw blocks [n][k/256][type size]; affine: uint32 [n][k*bits/32] */
+  int64_t weight_bytes;   /* size of weight_dev, checked against the shape */
+  const void *scales_dev; /* affine: [n][k/group_size] */
+  const void *biases_dev; /* affine: [n][k/group_size] */
+  const float *signs_dev; /* rotation signs [k] of +-1, or NULL for none */
+} ishi_weight_desc;
+
+/* ---- context ------------------------------------------------------------------------------ */
+
+/* One context per GPU and per stream of work. Allocates the library's tables and scratch. */
+ishi_status ishi_ctx_create(int device, ishi_ctx **out);
+void ishi_ctx_destroy(ishi_ctx *ctx);
+const char *ishi_status_string(ishi_status s);
+/* Text of the last failure seen through this context (valid until the next call). */
+const char *ishi_last_error(const ishi_ctx *ctx);
+/* Returns ISHI_E_TIMEOUT if any kernel launched through this context has reported that a
+ * bounded wait gave up since the last poll, else ISHI_OK. Does not synchronise. */
+ishi_status ishi_ctx_poll(ishi_ctx *ctx);
+/* Runtime switches, the counterpart of BonsaiRuntime.useVerifyMatmul and the tunables of
+ * VerifyMatmul (Sources/IshizukiKit/Core/RuntimeOptions.swift:43-54,
+ * Sources/IshizukiKit/Core/VerifyMatmul.swift:28-33). route: ISHI_ROUTE_*; crossover_rows:
+ * rows from which AUTO picks the tensor-core kernel (0 restores the built-in table). */
+ishi_status ishi_ctx_set_route(ishi_ctx *ctx, int route, int crossover_rows);
+
+/* ---- projection: PackedLinear ------------------------------------------------------------- */
+
+/* PackedLinear.init + VerifyMatmul.warm (Hadamard.swift:51-86, VerifyMatmul.swift:40-61):
+ * validates the weight, fixes the launch plan for its shape and allocates its scratch. */
+ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc,
+                                   ishi_projection **out);
+void ishi_projection_destroy(ishi_projection *p);
+int64_t ishi_projection_input_dim(const ishi_projection *p);  /* Projection.inputDim */
+int64_t ishi_projection_output_dim(const ishi_projection *p); /* Projection.outputDim */
+/* Compressed weight bytes one apply streams (codes + scales + biases, or GGUF blocks). */
+int64_t ishi_projection_weight_bytes(const ishi_projection *p);
+/* Rows from which this projection's AUTO route uses the tensor-core kernel; the counterpart of
+ * VerifyMatmul.minimumRows(bytes:) (VerifyMatmul.swift:19-26), re-measured for B200. */
+int ishi_projection_crossover_rows(const ishi_projection *p);
+
+/* PackedLinear.callAsFunction (Hadamard.swift:180-213): rotates x when the pack is rotated,
+ * then multiplies. rows in 1...16. */
+ishi_status ishi_projection_apply(ishi_projection *p, const void *x_dev, int rows, void *y_dev,
+                                  int64_t ldy, int flags, void *stream);
+/* PackedLinear.rotate (Hadamard.swift:235-243): xr = WHT_block(x * signs) / sqrt(block), fp16.
+ * Copies x when the projection has no rotation. */
+ishi_status ishi_projection_rotate(ishi_projection *p, const void *x_dev, int rows, void *xr_dev,
+                                   void *stream);
+/* PackedLinear.applyRotated (Hadamard.swift:245-252): multiplies an already rotated input. */
+ishi_status ishi_projection_apply_rotated(ishi_projection *p, const void *xr_dev, int rows,
+                                          void *y_dev, int64_t ldy, int flags, void *stream);
+/* The same product for a caller whose activations live in host memory: copies x in, multiplies,
+ * copies y out, all on the stream; returns once y_host is complete. */
+ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, int rows,
+                                       void *y_host, void *stream);
+
+/* ---- kernel level ------------------------------------------------------------------------- */
+
+/* GGMLKernels.matvec (Sources/IshizukiKit/Core/GGMLKernels.swift:177-213): x [rows, k] against
+ * the blocks of w [n, k], CUDA-core FMA with warp-shuffle reductions. rows in 1...16. */
+ishi_status ishi_ggml_matvec(ishi_ctx *ctx, const void *x_dev, int rows, const void *blocks_dev,
+                             int64_t blocks_bytes, int ggml_type, int64_t n, int64_t k,
+                             void *y_dev, void *stream);
+/* GGMLKernels.matmulFew (GGMLKernels.swift:219-253): the same product with each weight decoded
+ * once into a tensor-core fragment. The reference takes rows in 2...8; this takes 1...16. */
+ishi_status ishi_ggml_matmul_few(ishi_ctx *ctx, const void *x_dev, int rows,
+                                 const void *blocks_dev, int64_t blocks_bytes, int ggml_type,
+                                 int64_t n, int64_t k, void *y_dev, void *stream);
+/* GGMLKernels.dequantize (GGMLKernels.swift:60-95): blocks to a dense array, bit-exact to
+ * ggml's to_float. out_dtype ISHI_DT_F32, ISHI_DT_F16 or ISHI_DT_BF16. */
+ishi_status ishi_ggml_dequantize(ishi_ctx *ctx, int ggml_type, const void *blocks_dev,
+                                 int64_t n_blocks, void *out_dev, int out_dtype, void *stream);
+/* VerifyMatmul.applyAny (Sources/IshizukiKit/Core/VerifyMatmul.swift:73-120): x [rows, k]
+ * against an affine pack. route picks the kernel (ISHI_ROUTE_GEMV or ISHI_ROUTE_MMA). */
+ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x_dev, int rows, const void *w_dev,
+                               const void *scales_dev, const void *biases_dev, int scale_dtype,
+                               int group_size, int bits, int64_t n, int64_t k, int route,
+                               void *y_dev, void *stream);
+/* MLX dequantized(..., mode: .affine) as the reference's embedding path uses it
+ * (Hadamard.swift:378-381): w = float(code) * scale + bias, fp32 out [n, k]. */
+ishi_status ishi_affine_dequantize(ishi_ctx *ctx, const void *w_dev, const void *scales_dev,
+                                   const void *biases_dev, int scale_dtype, int group_size,
+                                   int bits, int64_t n, int64_t k, float *out_dev, void *stream);
+/* hadamardRotate(x, block:, signs:) forward form (Hadamard.swift:8-23). */
+ishi_status ishi_hadamard_rotate(ishi_ctx *ctx, const void *x_dev, int64_t rows, int64_t width,
+                                 int block, const float *signs_dev, void *y_dev, void *stream);
+/* VerifyMatmul.minimumRows(bytes:) exactly as the reference tabulates it for Apple M1
+ * (VerifyMatmul.swift:19-26); kept so a host can reproduce the reference's routing. */
+int ishi_reference_minimum_rows(int64_t bytes);
+/* GGMLType.blockSize / typeSize (GGUFFile.swift:44-80); 0 for a type this library lacks. */
+int ishi_ggml_block_size(int ggml_type);
+int ishi_ggml_type_size(int ggml_type);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ISHIZUKI_CUDA_H */

@@ -1,0 +1,79 @@
+"""ctypes binding of libishizuki_cuda.so: one Python signature per declaration in
+include/ishizuki_cuda.h. Loading fails loudly when the library is missing; there is no other
+implementation behind these names."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+
+from . import build as _build
+
+OK, E_INVALID, E_SHAPE, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_NOMEM = range(7)
+GGML_Q4_K, GGML_Q6_K, GGML_IQ2_XS = 12, 14, 17
+KIND_AFFINE, KIND_GGML = 0, 1
+DT_F16, DT_BF16, DT_F32 = 0, 1, 2
+ROUTE_AUTO, ROUTE_GEMV, ROUTE_MMA = 0, 1, 2
+OUT_TRANSPOSED = 1
+
+
+class WeightDesc(ctypes.Structure):
+    _fields_ = [
+        ("kind", c_int32), ("ggml_type", c_int32), ("bits", c_int32), ("group_size", c_int32),
+        ("scale_dtype", c_int32), ("hadamard_block", c_int32),
+        ("n", c_int64), ("k", c_int64),
+        ("weight_dev", c_void_p), ("weight_bytes", c_int64),
+        ("scales_dev", c_void_p), ("biases_dev", c_void_p), ("signs_dev", c_void_p),
+    ]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "ishi_ctx_create": (c_int, [c_int, POINTER(c_void_p)]),
+    "ishi_ctx_destroy": (None, [c_void_p]),
+    "ishi_status_string": (c_char_p, [c_int]),
+    "ishi_last_error": (c_char_p, [c_void_p]),
+    "ishi_ctx_poll": (c_int, [c_void_p]),
+    "ishi_ctx_set_route": (c_int, [c_void_p, c_int, c_int]),
+    "ishi_projection_create": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(c_void_p)]),
+    "ishi_projection_destroy": (None, [c_void_p]),
+    "ishi_projection_input_dim": (c_int64, [c_void_p]),
+    "ishi_projection_output_dim": (c_int64, [c_void_p]),
+    "ishi_projection_weight_bytes": (c_int64, [c_void_p]),
+    "ishi_projection_crossover_rows": (c_int, [c_void_p]),
+    "ishi_projection_apply": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
+    "ishi_projection_rotate": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "ishi_projection_apply_rotated": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
+    "ishi_projection_apply_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "ishi_ggml_matvec": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
+    "ishi_ggml_matmul_few": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
+    "ishi_ggml_dequantize": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p]),
+    "ishi_verify_matmul": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "ishi_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p]),
+    "ishi_hadamard_rotate": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "ishi_reference_minimum_rows": (c_int, [c_int64]),
+    "ishi_ggml_block_size": (c_int, [c_int]),
+    "ishi_ggml_type_size": (c_int, [c_int]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads (building first if the sources are newer) and types the C-ABI library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    if _build.stale():
+        try:
+            path = _build.build()
+        except RuntimeError:
+            if not path.exists():
+                raise
+    lib = ctypes.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,359 @@
+"""Host-side mirror of the reference's projection interface on top of the C ABI.
+
+The reference's host language is Swift; no Swift toolchain exists where this library is built
+and tested, so the same surface is written here in Python over ctypes (the Swift binding a
+maintainer would add is shown in INTEGRATION.md). Names, argument meaning and "declined"
+behaviour follow the reference:
+
+  GGMLType, GGUFBlocks      Sources/IshizukiKit/Config/GGUFFile.swift:13-121,
+                            Sources/IshizukiKit/Core/GGUFWeights.swift:13-26
+  GGMLKernels               Sources/IshizukiKit/Core/GGMLKernels.swift:60-95,146,177-253
+  VerifyMatmul              Sources/IshizukiKit/Core/VerifyMatmul.swift:11-120
+  PackedLinear              Sources/IshizukiKit/Core/Hadamard.swift:25-263
+  BonsaiRuntime             Sources/IshizukiKit/Core/RuntimeOptions.swift:43-54
+
+Where the reference returns nil ("declined, the caller falls back"), these return None for a
+shape guard and raise for anything else; there is no fallback path behind them. Device memory
+is held in torch tensors (plumbing only): every product is computed by libishizuki_cuda.so.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+
+class IshizukiError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{_status_name(status)}: {message}")
+        self.status = status
+
+
+def _status_name(status: int) -> str:
+    return _lib.load().ishi_status_string(status).decode()
+
+
+class GGMLType(enum.IntEnum):
+    """GGUF tensor types this library decodes, numbered as in the file format."""
+
+    q4K = 12
+    q6K = 14
+    iq2Xs = 17
+
+    @property
+    def blockSize(self) -> int:  # noqa: N802 (reference spelling)
+        return 256
+
+    @property
+    def typeSize(self) -> int:  # noqa: N802
+        return {12: 144, 14: 210, 17: 74}[int(self)]
+
+    @property
+    def isQuantized(self) -> bool:  # noqa: N802
+        return True
+
+    def byteCount(self, elements: int) -> int:  # noqa: N802
+        return elements // self.blockSize * self.typeSize
+
+
+@dataclass
+class GGUFBlocks:
+    """One tensor still in its GGML blocks: raw bytes (uint8, on the GPU), type, [N, K] shape."""
+
+    bytes: torch.Tensor
+    type: GGMLType
+    shape: tuple[int, int]
+
+    @property
+    def outputDim(self) -> int:  # noqa: N802
+        return self.shape[0]
+
+    @property
+    def inputDim(self) -> int:  # noqa: N802
+        return self.shape[-1]
+
+
+class BonsaiRuntime:
+    """Global switches the dispatch reads (reference: RuntimeOptions.swift:43-54)."""
+
+    useVerifyMatmul = True
+    # B200 additions: force one kernel family, or move the GEMV -> tensor-core crossover.
+    route = _lib.ROUTE_AUTO
+    crossoverRows = 0
+
+
+class Context:
+    """One per GPU; owns the library's tables and the scratch of the kernel-level calls."""
+
+    _by_device: dict[int, "Context"] = {}
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("ishizuki_b200 needs a CUDA device: there is no CPU path")
+        handle = ctypes.c_void_p()
+        rc = self.lib.ishi_ctx_create(device, ctypes.byref(handle))
+        if rc != _lib.OK:
+            raise IshizukiError(rc, f"ishi_ctx_create({device}) failed")
+        self.handle = handle
+        self.device = device
+
+    @classmethod
+    def get(cls, device: int | None = None) -> "Context":
+        device = torch.cuda.current_device() if device is None else device
+        ctx = cls._by_device.get(device)
+        if ctx is None:
+            ctx = cls._by_device[device] = Context(device)
+        return ctx
+
+    def last_error(self) -> str:
+        return self.lib.ishi_last_error(self.handle).decode()
+
+    def check(self, rc: int, declined=( _lib.E_SHAPE,)):
+        """OK -> True, a shape guard -> False (the reference's nil), anything else raises."""
+        if rc == _lib.OK:
+            return True
+        if rc in declined:
+            return False
+        raise IshizukiError(rc, self.last_error())
+
+    def poll(self) -> None:
+        rc = self.lib.ishi_ctx_poll(self.handle)
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.last_error())
+
+    def sync_route(self) -> None:
+        rc = self.lib.ishi_ctx_set_route(self.handle, BonsaiRuntime.route, BonsaiRuntime.crossoverRows)
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.last_error())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+_SCALE_DT = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16, torch.float32: _lib.DT_F32}
+_OUT_DT = _SCALE_DT
+
+
+def _as_half_rows(x: torch.Tensor) -> torch.Tensor | None:
+    if x.dim() != 2 or x.dtype != torch.float16 or not x.is_cuda:
+        return None
+    return x.contiguous()
+
+
+class GGMLKernels:
+    """Runs a tensor's GGML blocks on the GPU, expanded or folded into a product."""
+
+    matvecBatch = range(1, 17)
+    # The reference's few-row kernel takes 2...8 rows; this one takes every count the matvec does.
+    matmulFewRows = range(1, 17)
+
+    @staticmethod
+    def dequantize(blocks: torch.Tensor, type: GGMLType, shape, dtype=torch.bfloat16):
+        ctx = Context.get(blocks.device.index)
+        count = 1
+        for s in shape:
+            count *= s
+        try:
+            type = GGMLType(type)
+        except ValueError:
+            return None
+        if count % type.blockSize != 0:
+            return None
+        n_blocks = count // type.blockSize
+        if blocks.numel() < n_blocks * type.typeSize:
+            return None
+        out = torch.empty(count, dtype=dtype, device=blocks.device)
+        rc = ctx.lib.ishi_ggml_dequantize(ctx.handle, int(type), _ptr(blocks), n_blocks, _ptr(out),
+                                          _OUT_DT[dtype], _stream())
+        if not ctx.check(rc, declined=(_lib.E_SHAPE, _lib.E_UNSUPPORTED)):
+            return None
+        return out.reshape(tuple(shape))
+
+    @staticmethod
+    def _product(fn_name: str, x, blocks, type, outputDim):
+        x = _as_half_rows(x)
+        if x is None:
+            return None
+        try:
+            type = GGMLType(type)
+        except ValueError:
+            return None
+        ctx = Context.get(x.device.index)
+        m, k = x.shape
+        y = torch.empty((m, outputDim), dtype=torch.float16, device=x.device)
+        fn = getattr(ctx.lib, fn_name)
+        rc = fn(ctx.handle, _ptr(x), m, _ptr(blocks), blocks.numel(), int(type), outputDim, k, _ptr(y),
+                _stream())
+        return y if ctx.check(rc) else None
+
+    @staticmethod
+    def matvec(x, blocks: torch.Tensor, type: GGMLType, outputDim: int):  # noqa: N803
+        """x [M, K] against the blocks of w [N, K] on CUDA cores; None when declined."""
+        return GGMLKernels._product("ishi_ggml_matvec", x, blocks, type, outputDim)
+
+    @staticmethod
+    def matmulFew(x, blocks: torch.Tensor, type: GGMLType, outputDim: int, rowBlocks: int = 2):  # noqa: N802,N803
+        """The same product through tensor-core fragments. rowBlocks is accepted for source
+        compatibility; the tile shape is fixed by the launch plan here."""
+        return GGMLKernels._product("ishi_ggml_matmul_few", x, blocks, type, outputDim)
+
+
+class VerifyMatmul:
+    """A few-row affine matmul for the speculative verify."""
+
+    supportedRows = range(1, 17)  # the reference's Metal kernel stops at 8
+
+    @staticmethod
+    def minimumRows(bytes: int) -> int:  # noqa: N802,A002
+        """The reference's Apple-M1 crossover table, unchanged (VerifyMatmul.swift:19-26)."""
+        return int(_lib.load().ishi_reference_minimum_rows(bytes))
+
+    @staticmethod
+    def applyAny(x, w, scales, biases, groupSize: int, bits: int, route: int = _lib.ROUTE_MMA):  # noqa: N802,N803
+        x = _as_half_rows(x)
+        if x is None:
+            return None
+        ctx = Context.get(x.device.index)
+        m, k = x.shape
+        n = w.shape[0]
+        if w.shape[1] * 32 != k * bits or scales.dtype != biases.dtype:
+            return None
+        y = torch.empty((m, n), dtype=torch.float16, device=x.device)
+        rc = ctx.lib.ishi_verify_matmul(ctx.handle, _ptr(x), m, _ptr(w), _ptr(scales), _ptr(biases),
+                                        _SCALE_DT[scales.dtype], groupSize, bits, n, k, route, _ptr(y),
+                                        _stream())
+        return y if ctx.check(rc, declined=(_lib.E_SHAPE, _lib.E_UNSUPPORTED)) else None
+
+    @staticmethod
+    def apply(x, w, scales, biases, groupSize: int, bits: int):  # noqa: N803
+        if x.dim() != 2 or x.shape[0] not in VerifyMatmul.supportedRows:
+            return None
+        return VerifyMatmul.applyAny(x, w, scales, biases, groupSize, bits)
+
+
+class PackedLinear:
+    """A projection whose weight stays packed: GGUF blocks or an MLX affine pack, optionally
+    with a Hadamard-rotated input. Construct with the affine arguments or with ggml=GGUFBlocks."""
+
+    def __init__(self, weight=None, scales=None, biases=None, signs=None, block: int = 0,
+                 groupSize: int = 128, bits: int = 2, ggml: GGUFBlocks | None = None):  # noqa: N803
+        self.ggml = ggml
+        self.signs = signs
+        self.block = block
+        if ggml is not None:
+            self.weight = ggml.bytes
+            self.scales = self.biases = None
+            self.groupSize, self.bits = ggml.type.blockSize, 0
+            self.outputDim, self.inputDim = ggml.outputDim, ggml.inputDim
+        else:
+            self.weight, self.scales, self.biases = weight, scales, biases
+            self.groupSize, self.bits = groupSize, bits
+            self.outputDim = weight.shape[0]
+            self.inputDim = scales.shape[1] * groupSize
+            if block > 0 and signs is not None and signs.shape[0] != self.inputDim:
+                raise ValueError(f"sign vector is {signs.shape[0]} wide, expected {self.inputDim}")
+        if block > 0 and self.inputDim % block != 0:
+            raise ValueError(f"Hadamard block {block} does not divide input width {self.inputDim}")
+        self.ctx = Context.get(self.weight.device.index)
+        d = _lib.WeightDesc()
+        d.kind = _lib.KIND_GGML if ggml is not None else _lib.KIND_AFFINE
+        d.ggml_type = int(ggml.type) if ggml is not None else 0
+        d.bits, d.group_size = self.bits, self.groupSize
+        d.scale_dtype = _SCALE_DT[self.scales.dtype] if self.scales is not None else 0
+        d.hadamard_block = block
+        d.n, d.k = self.outputDim, self.inputDim
+        d.weight_dev = self.weight.data_ptr()
+        d.weight_bytes = self.weight.numel() * self.weight.element_size()
+        d.scales_dev = 0 if self.scales is None else self.scales.data_ptr()
+        d.biases_dev = 0 if self.biases is None else self.biases.data_ptr()
+        d.signs_dev = 0 if signs is None else signs.data_ptr()
+        handle = ctypes.c_void_p()
+        rc = self.ctx.lib.ishi_projection_create(self.ctx.handle, ctypes.byref(d), ctypes.byref(handle))
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+        self.handle = handle
+
+    def __del__(self):
+        handle = getattr(self, "handle", None)
+        if handle:
+            self.ctx.lib.ishi_projection_destroy(handle)
+            self.handle = None
+
+    @property
+    def weightBytes(self) -> int:  # noqa: N802
+        return int(self.ctx.lib.ishi_projection_weight_bytes(self.handle))
+
+    @property
+    def crossoverRows(self) -> int:  # noqa: N802
+        return int(self.ctx.lib.ishi_projection_crossover_rows(self.handle))
+
+    def _rows(self, x: torch.Tensor) -> tuple[torch.Tensor, tuple[int, ...]]:
+        if x.dtype != torch.float16 or not x.is_cuda:
+            raise TypeError("activations must be fp16 CUDA tensors")
+        shape = tuple(x.shape)
+        return x.reshape(-1, shape[-1]).contiguous(), shape
+
+    def _out(self, h: torch.Tensor, transposed: bool) -> torch.Tensor:
+        m = h.shape[0]
+        if transposed:
+            return torch.empty((self.outputDim, m), dtype=torch.float16, device=h.device)
+        return torch.empty((m, self.outputDim), dtype=torch.float16, device=h.device)
+
+    def __call__(self, x: torch.Tensor, transposed: bool = False, out: torch.Tensor | None = None):
+        """y = x . W^T for 1...16 rows of x, rotating x first when the pack is rotated."""
+        self.ctx.sync_route()
+        h, shape = self._rows(x)
+        y = self._out(h, transposed) if out is None else out
+        rc = self.ctx.lib.ishi_projection_apply(self.handle, _ptr(h), h.shape[0], _ptr(y), y.stride(0),
+                                                _lib.OUT_TRANSPOSED if transposed else 0, _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+        return y if transposed or out is not None else y.reshape(shape[:-1] + (self.outputDim,))
+
+    def rotate(self, x: torch.Tensor) -> torch.Tensor:
+        h, shape = self._rows(x)
+        xr = torch.empty_like(h)
+        rc = self.ctx.lib.ishi_projection_rotate(self.handle, _ptr(h), h.shape[0], _ptr(xr), _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+        return xr.reshape(shape)
+
+    def applyRotated(self, h: torch.Tensor) -> torch.Tensor:  # noqa: N802
+        self.ctx.sync_route()
+        rows, shape = self._rows(h)
+        y = self._out(rows, False)
+        rc = self.ctx.lib.ishi_projection_apply_rotated(self.handle, _ptr(rows), rows.shape[0], _ptr(y),
+                                                        y.stride(0), 0, _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+        return y.reshape(shape[:-1] + (self.outputDim,))
+
+    def apply_host(self, x_host, y_host) -> None:
+        """Host-buffer form: x_host [M, K] and y_host [M, N] are C-contiguous fp16 numpy arrays."""
+        rc = self.ctx.lib.ishi_projection_apply_host(
+            self.handle, x_host.ctypes.data_as(ctypes.c_void_p), x_host.shape[0],
+            y_host.ctypes.data_as(ctypes.c_void_p), _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+
+
+def hadamardRotate(x: torch.Tensor, block: int, signs: torch.Tensor | None) -> torch.Tensor:  # noqa: N802
+    """xr = WHT_block(x * signs) / sqrt(block) along the last axis (forward form only)."""
+    ctx = Context.get(x.device.index)
+    h = x.reshape(-1, x.shape[-1]).contiguous()
+    y = torch.empty_like(h)
+    rc = ctx.lib.ishi_hadamard_rotate(ctx.handle, _ptr(h), h.shape[0], h.shape[1], block, _ptr(signs), _ptr(y),
+                                      _stream())
+    if rc != _lib.OK:
+        raise IshizukiError(rc, ctx.last_error())
+    return y.reshape(x.shape)
