@@ -14,6 +14,7 @@
 #include "dequant.cuh"
 #include "fmt_q4k.cuh"
 #include "ishi_stream.cuh"
+#include "rfmt_q4k.cuh"
 
 using namespace ishi;
 
@@ -139,6 +140,53 @@ bool make_plan(const ishi_ctx *ctx, int fmt, long long N, long long K, int rows,
   return true;
 }
 
+// Launch plan of the tcgen05 kernel (rows 1...8): two CTAs per SM, 128-row panels, kc units per
+// stage, the weight read from its tiled copy.
+struct RowPlan {
+  bool ok = false;
+  int units = 0, P = 0, SL = 2, kc = 2, nstages = 2, x_off = 0, bmin_off = 0, stage_bytes = 0;
+  int grid = 0, nsrc = 0;
+  int tile_bytes = 0, sec_off[kMaxSrc] = {0, 0, 0}, unit_bytes[kMaxSrc] = {0, 0, 0};
+  size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
+};
+
+bool make_row_plan(const ishi_ctx *ctx, long long N, long long K, int nsrc, const int *unit_bytes, RowPlan *pl) {
+  pl->units = (int)(K / 256);
+  pl->P = (int)((N + kRowPanel - 1) / kRowPanel);
+  pl->grid = 2 * ctx->sm_count;
+  pl->nsrc = nsrc;
+  int tile = 0;
+  for (int i = 0; i < nsrc; ++i) {
+    pl->sec_off[i] = tile;
+    pl->unit_bytes[i] = unit_bytes[i];
+    tile += kRowPanel * unit_bytes[i];  // a multiple of 128 bytes
+  }
+  pl->tile_bytes = tile;
+  pl->tiles_bytes = (size_t)pl->P * pl->units * tile;
+  const size_t half_sm = (size_t)(std::min(kSmemBudget, ctx->smem_optin) - 2048) / 2;
+  // two units a stage when they fit twice, else one
+  for (pl->kc = pl->units >= 2 ? 2 : 1; pl->kc >= 1; --pl->kc) {
+    pl->x_off = pl->kc * tile;
+    pl->bmin_off = pl->x_off + pl->kc * 4096;
+    pl->stage_bytes = pl->bmin_off + pl->kc * 512;
+    if (128 + 2 * (size_t)pl->stage_bytes <= half_sm) break;
+  }
+  if (pl->kc < 1) return false;
+  int nst = 4;
+  for (; nst >= 2; --nst) {
+    pl->smem = 128 + (size_t)nst * pl->stage_bytes;
+    if (pl->smem <= half_sm) break;
+  }
+  pl->nstages = nst;
+  const long long Q = (long long)pl->P * pl->units;
+  const int dense_slots = (pl->grid + pl->P - 1) / pl->P + 1;
+  pl->SL = Q >= pl->grid ? dense_slots : std::max(pl->units, dense_slots);
+  pl->scratch_floats = (size_t)pl->P * pl->SL * 8 * kRowPanel;
+  pl->counters = (size_t)pl->P * 4;
+  pl->ok = true;
+  return true;
+}
+
 ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t counters) {
   if (floats > ws->scratch_floats) {
     if (ws->scratch) cudaFree(ws->scratch);
@@ -174,6 +222,24 @@ ishi_status launch_stream(ishi_ctx *ctx, const Plan &pl, const StreamArgs &args,
   const int grid = pl.Gc * pl.S;
   const int block = (pl.W + 1) * 32;
   kern<<<grid, block, pl.smem, st>>>(args);
+  ISHI_CUDA(ctx, cudaGetLastError());
+  return ISHI_OK;
+}
+
+template <class Fmt>
+ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
+  auto kern = rowstream_kernel<Fmt>;
+  static bool configured[64] = {false};
+  static std::mutex once;
+  {
+    std::lock_guard<std::mutex> g(once);
+    if (!configured[ctx->device & 63]) {
+      ISHI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (std::min(kSmemBudget, ctx->smem_optin) - 2048) / 2));
+      configured[ctx->device & 63] = true;
+    }
+  }
+  kern<<<pl.grid, kRowThreads, pl.smem, st>>>(args);
   ISHI_CUDA(ctx, cudaGetLastError());
   return ISHI_OK;
 }
@@ -225,6 +291,45 @@ ishi_status run_ggml_mma(ishi_ctx *ctx, const Plan &pl, Workspace *ws, const Ggm
       return fail(ctx, ISHI_E_UNSUPPORTED, "no matmul kernel for GGML type %d", c.type);
   }
 }
+
+ishi_status run_row(ishi_ctx *ctx, const RowPlan &pl, Workspace *ws, const uint8_t *tiles, int fmt, const void *x,
+                    int rows, long long n, long long k, void *y, long long ldy, int flags, int group_size,
+                    int scale_dtype, cudaStream_t st) {
+  RowArgs a;
+  memset(&a, 0, sizeof(a));
+  a.tiles = tiles;
+  a.tile_bytes = pl.tile_bytes;
+  for (int i = 0; i < kMaxSrc; ++i) {
+    a.sec_off[i] = pl.sec_off[i];
+    a.unit_bytes[i] = pl.unit_bytes[i];
+  }
+  a.x = static_cast<const __half *>(x);
+  a.y = static_cast<__half *>(y);
+  a.ldy = ldy;
+  a.out_transposed = (flags & ISHI_OUT_TRANSPOSED) ? 1 : 0;
+  a.scratch = ws->scratch;
+  a.counters = ws->counters;
+  a.err = ctx->err_dev;
+  a.M = rows;
+  a.N = (int)n;
+  a.K = (int)k;
+  a.units = pl.units;
+  a.P = pl.P;
+  a.SL = pl.SL;
+  a.kc = pl.kc;
+  a.nstages = pl.nstages;
+  a.x_off = pl.x_off;
+  a.bmin_off = pl.bmin_off;
+  a.stage_bytes = pl.stage_bytes;
+  a.group_size = group_size;
+  a.scale_dtype = scale_dtype;
+  switch (fmt) {
+    case ISHI_GGML_Q4_K: return launch_row<RowQ4K>(ctx, pl, a, st);
+    default: return fail(ctx, ISHI_E_UNSUPPORTED, "no tcgen05 kernel for format %d", fmt);
+  }
+}
+
+bool has_row_kernel(int fmt) { return fmt == ISHI_GGML_Q4_K; }
 
 ishi_status check_ggml_call(ishi_ctx *ctx, const GgmlCall &c, long long blocks_bytes, int max_rows) {
   if (!ctx) return ISHI_E_INVALID;
@@ -449,7 +554,10 @@ ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *, int, const void *, c
 struct ishi_projection {
   ishi_ctx *ctx = nullptr;
   ishi_weight_desc d;
-  Plan plan[2];       // rows 1..8 and rows 9..16
+  Plan plan[2];       // warp-level kernel: rows 1..8 and rows 9..16
+  RowPlan row;        // tcgen05 kernel: rows 1..8
+  uint8_t *tiles = nullptr;  // the weight re-tiled for the tcgen05 kernel (library-owned)
+  int fmt = 0;
   Workspace ws;       // this projection's own scratch, so apply never allocates
   __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
   int64_t weight_bytes = 0;
@@ -469,6 +577,8 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   const Plan &pl = p->plan[rows > 8 ? 1 : 0];
   if (p->d.kind == ISHI_KIND_GGML) {
     GgmlCall c{x, rows, p->d.weight_dev, p->d.ggml_type, p->d.n, p->d.k, y, ldy, flags};
+    if (rows <= 8 && p->row.ok && ctx->route != ISHI_ROUTE_GEMV)
+      return run_row(ctx, p->row, &p->ws, p->tiles, p->fmt, x, rows, p->d.n, p->d.k, y, ldy, flags, 0, 0, st);
     return run_ggml_mma(ctx, pl, &p->ws, c, st);
   }
   return fail(ctx, ISHI_E_UNSUPPORTED, "affine kernel not built yet");
@@ -537,7 +647,36 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
     }
     floats = std::max(floats, p->plan[i].scratch_floats);
   }
-  ishi_status s = ensure_workspace(ctx, &p->ws, floats, (size_t)p->plan[0].P);
+  size_t counters = (size_t)p->plan[0].P;
+  p->fmt = fmt;
+  if (has_row_kernel(fmt) && make_row_plan(ctx, d.n, d.k, nsrc, unit_bytes, &p->row)) {
+    floats = std::max(floats, p->row.scratch_floats);
+    counters = std::max(counters, p->row.counters);
+  }
+  ishi_status s = ensure_workspace(ctx, &p->ws, floats, counters);
+  if (s == ISHI_OK && p->row.ok) {
+    // re-tile the weight once; the caller's buffer stays as it is and is still used for 9...16 rows
+    cudaError_t e = cudaMalloc(&p->tiles, p->row.tiles_bytes);
+    if (e != cudaSuccess) {
+      s = fail(ctx, ISHI_E_CUDA, "cudaMalloc(tiled weight, %zu bytes): %s", p->row.tiles_bytes, cudaGetErrorString(e));
+    } else {
+      TileSrc ts[kMaxSrc];
+      memset(ts, 0, sizeof(ts));
+      const void *bases[kMaxSrc] = {d.weight_dev, d.scales_dev, d.biases_dev};
+      for (int i = 0; i < nsrc; ++i) {
+        ts[i].base = static_cast<const uint8_t *>(bases[i]);
+        ts[i].unit_bytes = unit_bytes[i];
+        ts[i].row_bytes = (long long)(d.k / 256) * unit_bytes[i];
+        ts[i].sec_off = p->row.sec_off[i];
+      }
+      const long long triples = (long long)p->row.P * p->row.units * kRowPanel;
+      const int grid = (int)std::min<long long>((triples + 255) / 256, (long long)ctx->sm_count * 16);
+      prepare_tiles_kernel<<<grid, 256>>>(ts[0], ts[1], ts[2], nsrc, d.n, p->row.units, p->row.tile_bytes, p->tiles);
+      e = cudaGetLastError();
+      if (e == cudaSuccess) e = cudaDeviceSynchronize();
+      if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "tiling the weight: %s", cudaGetErrorString(e));
+    }
+  }
   if (s == ISHI_OK && d.hadamard_block != 0) {
     cudaError_t e = cudaMalloc(&p->xr, (size_t)16 * d.k * sizeof(__half));
     if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "cudaMalloc(rotated x): %s", cudaGetErrorString(e));
@@ -556,6 +695,7 @@ void ishi_projection_destroy(ishi_projection *p) {
   if (p->ws.scratch) cudaFree(p->ws.scratch);
   if (p->ws.counters) cudaFree(p->ws.counters);
   if (p->xr) cudaFree(p->xr);
+  if (p->tiles) cudaFree(p->tiles);
   delete p;
 }
 

@@ -69,32 +69,43 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
 }
 
 // ---- shared memory loads ----------------------------------------------------------------------
+// The weight loads are plain (non-volatile) asm so the compiler may interleave them with the
+// tensor-core work of earlier chunks. Ordering against the barriers that guard a stage comes
+// from data dependences instead: stage_acquire() makes the stage address depend on the wait that
+// precedes it, and values_ready() pins every value computed from the stage before its release.
+__device__ __forceinline__ uint32_t stage_acquire(uint32_t addr) {
+  asm volatile("" : "+r"(addr)::"memory");
+  return addr;
+}
+__device__ __forceinline__ void values_ready(float &a, float &b, float &c, float &d) {
+  asm volatile("" : "+f"(a), "+f"(b), "+f"(c), "+f"(d)::"memory");
+}
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "r"(addr));
   return v;
 }
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
   uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ uint32_t lds8(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
 __device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
@@ -117,7 +128,7 @@ __device__ __forceinline__ float4 lds128f(uint32_t addr) {
 //   c0, c1 = C[g][2t, 2t+1]   c2, c3 = C[g+8][2t, 2t+1]
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])

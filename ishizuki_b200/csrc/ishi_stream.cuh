@@ -28,7 +28,7 @@ namespace ishi {
 
 constexpr int kMaxSrc = 3;
 constexpr int kPanelRows = 16;
-constexpr int kMaxConsumerWarps = 12;  // plus one producer warp: 416 threads, up to 152 registers each
+constexpr int kMaxConsumerWarps = 11;  // plus one producer warp: 384 threads, 168 registers each
 
 struct StreamSrc {
   const uint8_t *base;   // row 0 of this byte stream, 16-byte aligned
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) stream_kernel
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
 
-        const uint32_t stage = stage_base0 + (uint32_t)s * stage_bytes;
+        const uint32_t stage = stage_acquire(stage_base0 + (uint32_t)s * stage_bytes);
         const long long row0 = (long long)p * kPanelRows + g;
 #pragma unroll
         for (int q = 0; q < UW; ++q) {
@@ -226,6 +226,8 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1) stream_kernel
             Fmt::template unit<MT, UW>(acc, xf, q, a, stage, row0, ub0 + ua, u - ua, g, t);
           }
         }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) values_ready(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
 
