@@ -1,5 +1,5 @@
-// C ABI of the verify-matmul library: argument validation, per-shape launch plans, the
-// row-count crossover and the kernel launches. No torch, no NCCL, no CPU fallback: a shape
+// C ABI of the verify-matmul library: argument validation, per-shape launch plans, the one-time
+// re-tiling of weights and the kernel launches. No torch, no NCCL, no CPU fallback: a shape
 // without a kernel is an error status.
 #include <cuda_runtime.h>
 
@@ -12,21 +12,35 @@
 
 #include "../../include/ishizuki_cuda.h"
 #include "dequant.cuh"
-#include "fmt_q4k.cuh"
-#include "ishi_stream.cuh"
+#include "ishi_rowstream.cuh"
+#include "rfmt_affine.cuh"
+#include "rfmt_iq2xs.cuh"
 #include "rfmt_q4k.cuh"
+#include "rfmt_q6k.cuh"
 
 using namespace ishi;
 
 namespace {
 
-constexpr int kSmemBudget = 227 * 1024 - 512;  // dynamic part; the kernels also hold a few static bytes
+constexpr int kSmemPerSm = 227 * 1024;
 
 struct Workspace {
   float *scratch = nullptr;
   unsigned int *counters = nullptr;
-  size_t scratch_floats = 0;
-  size_t n_counters = 0;
+  uint8_t *tiles = nullptr;  // kernel-level calls re-tile the weight here on every call
+  size_t scratch_floats = 0, n_counters = 0, tiles_bytes = 0;
+};
+
+// Internal format id: the GGML type number, or 100 + bits for an affine pack.
+int format_of(const ishi_weight_desc &d) { return d.kind == ISHI_KIND_GGML ? d.ggml_type : 100 + d.bits; }
+
+struct RowPlan {
+  bool ok = false;
+  int units = 0, P = 0, SL = 2, kc = 2, nstages = 2, x_off = 0, bmin_off = 0, xs_off = 0, stage_bytes = 0;
+  int grid = 0, nsec = 0, table_bytes = 0;
+  int tile_bytes = 0, sec_off[4] = {0, 0, 0, 0}, sec_bytes[4] = {0, 0, 0, 0};
+  TileSrc src[4];
+  size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
 };
 
 }  // namespace
@@ -39,7 +53,7 @@ struct ishi_ctx {
   int crossover_rows = 0;
   int *err_host = nullptr;  // mapped pinned word the kernels raise on a timed-out wait
   int *err_dev = nullptr;
-  Workspace ws;             // for the kernel-level entry points
+  Workspace ws;                             // for the kernel-level entry points
   void *pin_x = nullptr, *pin_y = nullptr;  // pinned staging for apply_host
   void *dev_x = nullptr, *dev_y = nullptr;
   size_t pin_x_bytes = 0, pin_y_bytes = 0;
@@ -47,21 +61,17 @@ struct ishi_ctx {
   char last_error[256] = {0};
 };
 
-namespace {
-
-struct Plan;
-
-}  // namespace
-
-namespace {
-
-struct Plan {
-  int fmt = 0;  // ggml type, or 100 + bits for affine
-  int units = 0, S = 1, P = 0, Gc = 1, SL = 2, W = 1, UW = 1, MT = 1, nstages = 2, row_stride = 0;
-  int seg_off[kMaxSrc] = {0, 0, 0};
-  size_t smem = 0;
-  size_t scratch_floats = 0;
+struct ishi_projection {
+  ishi_ctx *ctx = nullptr;
+  ishi_weight_desc d;
+  int fmt = 0;
+  RowPlan plan;
+  Workspace ws;          // this projection's own scratch and tiled weight: apply never allocates
+  __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
+  int64_t weight_bytes = 0;
 };
+
+namespace {
 
 ishi_status fail(ishi_ctx *ctx, ishi_status s, const char *fmt, ...) {
   if (ctx) {
@@ -73,11 +83,10 @@ ishi_status fail(ishi_ctx *ctx, ishi_status s, const char *fmt, ...) {
   return s;
 }
 
-#define ISHI_CUDA(ctx, call)                                                             \
-  do {                                                                                   \
-    cudaError_t e_ = (call);                                                             \
-    if (e_ != cudaSuccess)                                                               \
-      return fail(ctx, ISHI_E_CUDA, "%s: %s", #call, cudaGetErrorString(e_));            \
+#define ISHI_CUDA(ctx, call)                                                                       \
+  do {                                                                                             \
+    cudaError_t e_ = (call);                                                                       \
+    if (e_ != cudaSuccess) return fail(ctx, ISHI_E_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
   } while (0)
 
 int type_size(int t) {
@@ -91,90 +100,119 @@ int type_size(int t) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Fixes the grid, the K split and the shared-memory ring for one (format, N, K, rows) shape.
-// unit_bytes[i] are the per-row bytes of each byte stream for one 256-wide unit.
-bool make_plan(const ishi_ctx *ctx, int fmt, long long N, long long K, int rows, int nsrc,
-               const int *unit_bytes, int row_skew, Plan *pl) {
-  pl->fmt = fmt;
-  pl->MT = rows > 8 ? 2 : 1;
-  pl->UW = rows > 8 ? 1 : 2;
-  pl->units = (int)(K / 256);
-  pl->P = (int)((N + kPanelRows - 1) / kPanelRows);
-  const int cap = kMaxConsumerWarps * pl->UW;
-  const int smin = (pl->units + cap - 1) / cap;
-  // Among the few smallest workable splits take the one that occupies the most SMs.
-  int best_s = smin, best_g = 0;
-  for (int s = smin; s <= std::min(pl->units, smin + 3); ++s) {
-    if (s > ctx->sm_count) break;
-    const int g = (ctx->sm_count / s) * s;
-    if (g > best_g) {
-      best_g = g;
-      best_s = s;
-    }
+// The reference's shape guards plus this library's own (Sources/IshizukiKit/Core/VerifyMatmul.swift
+// :78-87, Sources/IshizukiKit/Core/GGMLKernels.swift:181-189,223-230). Fills weight_bytes.
+ishi_status check_desc(ishi_ctx *ctx, const ishi_weight_desc &d, int64_t *weight_bytes) {
+  if (!d.weight_dev || (reinterpret_cast<uintptr_t>(d.weight_dev) & 3u))
+    return fail(ctx, ISHI_E_INVALID, "weight pointer null or not 4-byte aligned");
+  if (d.n <= 0 || d.k <= 0) return fail(ctx, ISHI_E_SHAPE, "n and k must be positive");
+  if (d.n > (1ll << 31) - 256 || d.k > (1ll << 30)) return fail(ctx, ISHI_E_SHAPE, "shape too large");
+  if (d.k % 256 != 0) return fail(ctx, ISHI_E_SHAPE, "k %lld is not a whole number of 256-wide blocks", (long long)d.k);
+  if (d.hadamard_block != 0) {
+    const int b = d.hadamard_block;
+    if (b < 0 || (b & (b - 1)) != 0 || b > 8192 || d.k % b != 0)
+      return fail(ctx, ISHI_E_SHAPE, "Hadamard block %d does not divide input width %lld", b, (long long)d.k);
   }
-  pl->S = best_s;
-  pl->Gc = std::max(1, ctx->sm_count / pl->S);
-  const int umax = (pl->units + pl->S - 1) / pl->S;
-  pl->W = (umax + pl->UW - 1) / pl->UW;
-  const int dense_slots = (pl->Gc + pl->P - 1) / pl->P + 1;
-  pl->SL = (long long)pl->P * (pl->units / pl->S) >= pl->Gc ? dense_slots : std::max(umax, dense_slots);
-  int need = 0;
-  for (int i = 0; i < nsrc; ++i) {
-    pl->seg_off[i] = need;
-    need += (umax * unit_bytes[i] + 30 + 15) & ~15;
+  int64_t bytes = 0, total = 0;
+  if (d.kind == ISHI_KIND_GGML) {
+    const int ts = type_size(d.ggml_type);
+    if (ts == 0) return fail(ctx, ISHI_E_UNSUPPORTED, "GGML type %d has no decoder here", d.ggml_type);
+    bytes = total = d.n * (d.k / 256) * ts;
+  } else if (d.kind == ISHI_KIND_AFFINE) {
+    if (d.bits < 2 || d.bits > 8) return fail(ctx, ISHI_E_SHAPE, "affine width %d outside 2...8", d.bits);
+    if (d.bits != 2 && d.bits != 4 && d.bits != 8)
+      return fail(ctx, ISHI_E_UNSUPPORTED, "affine width %d has no kernel here", d.bits);
+    if (d.group_size != 32 && d.group_size != 64 && d.group_size != 128)
+      return fail(ctx, ISHI_E_SHAPE, "group size %d outside {32, 64, 128}", d.group_size);
+    if (d.scale_dtype < ISHI_DT_F16 || d.scale_dtype > ISHI_DT_F32) return fail(ctx, ISHI_E_INVALID, "bad scale dtype");
+    if (!d.scales_dev || !d.biases_dev || (reinterpret_cast<uintptr_t>(d.scales_dev) & 3u) ||
+        (reinterpret_cast<uintptr_t>(d.biases_dev) & 3u))
+      return fail(ctx, ISHI_E_INVALID, "scales/biases null or misaligned");
+    const int sb = d.scale_dtype == ISHI_DT_F32 ? 4 : 2;
+    bytes = d.n * d.k * d.bits / 8;
+    total = bytes + 2 * d.n * (d.k / d.group_size) * sb;
+  } else {
+    return fail(ctx, ISHI_E_INVALID, "bad weight kind %d", d.kind);
   }
-  int stride = (need + 127) / 128 * 128 + row_skew;
-  if (stride - 128 >= need) stride -= 128;
-  pl->row_stride = stride;
-  const size_t stage = (size_t)kPanelRows * stride;
-  int nst = 8;
-  for (; nst >= 2; --nst) {
-    const size_t bars = ((size_t)(2 * nst + nst + 1) * 8 + 127) & ~(size_t)127;
-    const size_t red = (size_t)(nst + 1) * pl->W * pl->MT * 512;
-    pl->smem = bars + red + nst * stage;
-    if (pl->smem <= (size_t)std::min(kSmemBudget, ctx->smem_optin)) break;
-  }
-  if (nst < 2) return false;
-  pl->nstages = nst;
-  pl->scratch_floats = (size_t)pl->P * pl->S * pl->SL * 2 /* room for 16 rows */ * 128;
-  return true;
+  if (d.weight_bytes < bytes)
+    return fail(ctx, ISHI_E_SHAPE, "weight buffer holds %lld bytes, shape needs %lld", (long long)d.weight_bytes,
+                (long long)bytes);
+  *weight_bytes = total;
+  return ISHI_OK;
 }
 
-// Launch plan of the tcgen05 kernel (rows 1...8): two CTAs per SM, 128-row panels, kc units per
-// stage, the weight read from its tiled copy.
-struct RowPlan {
-  bool ok = false;
-  int units = 0, P = 0, SL = 2, kc = 2, nstages = 2, x_off = 0, bmin_off = 0, stage_bytes = 0;
-  int grid = 0, nsrc = 0;
-  int tile_bytes = 0, sec_off[kMaxSrc] = {0, 0, 0}, unit_bytes[kMaxSrc] = {0, 0, 0};
-  size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
-};
-
-bool make_row_plan(const ishi_ctx *ctx, long long N, long long K, int nsrc, const int *unit_bytes, RowPlan *pl) {
-  pl->units = (int)(K / 256);
-  pl->P = (int)((N + kRowPanel - 1) / kRowPanel);
-  pl->grid = 2 * ctx->sm_count;
-  pl->nsrc = nsrc;
-  int tile = 0;
-  for (int i = 0; i < nsrc; ++i) {
-    pl->sec_off[i] = tile;
-    pl->unit_bytes[i] = unit_bytes[i];
-    tile += kRowPanel * unit_bytes[i];  // a multiple of 128 bytes
+// Sections of a tile for each format: which field of the source goes where.
+void describe_sections(const ishi_weight_desc &d, RowPlan *pl) {
+  const uint8_t *w = static_cast<const uint8_t *>(d.weight_dev);
+  const long long units = d.k / 256;
+  auto sec = [&](int i, const uint8_t *base, long long row_bytes, int unit_stride, int field) {
+    pl->src[i].base = base;
+    pl->src[i].row_bytes = row_bytes;
+    pl->src[i].unit_stride = unit_stride;
+    pl->src[i].field_bytes = field;
+  };
+  memset(pl->src, 0, sizeof(pl->src));
+  if (d.kind == ISHI_KIND_GGML) {
+    const int ts = type_size(d.ggml_type);
+    const long long rb = units * ts;
+    switch (d.ggml_type) {
+      case ISHI_GGML_Q4_K:
+        pl->nsec = 1;
+        sec(0, w, rb, ts, 144);
+        break;
+      case ISHI_GGML_Q6_K:
+        pl->nsec = 4;
+        sec(0, w, rb, ts, 128);       // ql
+        sec(1, w + 128, rb, ts, 64);  // qh
+        sec(2, w + 192, rb, ts, 16);  // scales
+        sec(3, w + 208, rb, ts, 2);   // d
+        break;
+      default:  // IQ2_XS
+        pl->nsec = 3;
+        sec(0, w + 2, rb, ts, 64);  // index words
+        sec(1, w + 66, rb, ts, 8);  // scale bytes
+        sec(2, w, rb, ts, 2);       // d
+        break;
+    }
+  } else {
+    const int sb = d.scale_dtype == ISHI_DT_F32 ? 4 : 2;
+    const int per_unit = 256 / d.group_size;
+    pl->nsec = 3;
+    sec(0, w, d.k * d.bits / 8, 32 * d.bits, 32 * d.bits);
+    sec(1, static_cast<const uint8_t *>(d.scales_dev), (d.k / d.group_size) * sb, per_unit * sb, per_unit * sb);
+    sec(2, static_cast<const uint8_t *>(d.biases_dev), (d.k / d.group_size) * sb, per_unit * sb, per_unit * sb);
   }
-  pl->tile_bytes = tile;
-  pl->tiles_bytes = (size_t)pl->P * pl->units * tile;
-  const size_t half_sm = (size_t)(std::min(kSmemBudget, ctx->smem_optin) - 2048) / 2;
-  // two units a stage when they fit twice, else one
+  int off = 0;
+  for (int i = 0; i < pl->nsec; ++i) {
+    pl->src[i].sec_off = pl->sec_off[i] = off;
+    pl->sec_bytes[i] = pl->src[i].field_bytes;
+    off += kRowPanel * pl->src[i].field_bytes;  // a multiple of 256 bytes
+  }
+  pl->tile_bytes = off;
+}
+
+// Fixes grid, stage ring and scratch for one weight: two CTAs per SM, 128-row panels, kc units
+// per stage.
+bool make_row_plan(const ishi_ctx *ctx, const ishi_weight_desc &d, RowPlan *pl) {
+  describe_sections(d, pl);
+  pl->units = (int)(d.k / 256);
+  pl->P = (int)((d.n + kRowPanel - 1) / kRowPanel);
+  pl->grid = 2 * ctx->sm_count;
+  pl->table_bytes = (d.kind == ISHI_KIND_GGML && d.ggml_type == ISHI_GGML_IQ2_XS) ? RowIQ2XS::kTableBytes : 0;
+  pl->tiles_bytes = (size_t)pl->P * pl->units * pl->tile_bytes;
+  const size_t half_sm = (size_t)(std::min(kSmemPerSm, ctx->smem_optin) - 4096) / 2;
+  const size_t fixed = 128 + (size_t)pl->table_bytes;
   for (pl->kc = pl->units >= 2 ? 2 : 1; pl->kc >= 1; --pl->kc) {
-    pl->x_off = pl->kc * tile;
+    pl->x_off = pl->kc * pl->tile_bytes;
     pl->bmin_off = pl->x_off + pl->kc * 4096;
-    pl->stage_bytes = pl->bmin_off + pl->kc * 512;
-    if (128 + 2 * (size_t)pl->stage_bytes <= half_sm) break;
+    pl->xs_off = pl->bmin_off + pl->kc * 512;
+    pl->stage_bytes = pl->xs_off + pl->kc * 256;
+    if (fixed + 2 * (size_t)pl->stage_bytes <= half_sm) break;
   }
   if (pl->kc < 1) return false;
   int nst = 4;
   for (; nst >= 2; --nst) {
-    pl->smem = 128 + (size_t)nst * pl->stage_bytes;
+    pl->smem = fixed + (size_t)nst * pl->stage_bytes;
     if (pl->smem <= half_sm) break;
   }
   pl->nstages = nst;
@@ -187,7 +225,7 @@ bool make_row_plan(const ishi_ctx *ctx, long long N, long long K, int nsrc, cons
   return true;
 }
 
-ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t counters) {
+ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t counters, size_t tiles) {
   if (floats > ws->scratch_floats) {
     if (ws->scratch) cudaFree(ws->scratch);
     ws->scratch = nullptr;
@@ -203,25 +241,28 @@ ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t
     ISHI_CUDA(ctx, cudaMemset(ws->counters, 0, counters * sizeof(unsigned int)));
     ws->n_counters = counters;
   }
+  if (tiles > ws->tiles_bytes) {
+    if (ws->tiles) cudaFree(ws->tiles);
+    ws->tiles = nullptr;
+    ws->tiles_bytes = 0;
+    ISHI_CUDA(ctx, cudaMalloc(&ws->tiles, tiles));
+    ws->tiles_bytes = tiles;
+  }
   return ISHI_OK;
 }
 
-template <class Fmt, int MT, int UW>
-ishi_status launch_stream(ishi_ctx *ctx, const Plan &pl, const StreamArgs &args, cudaStream_t st) {
-  auto kern = stream_kernel<Fmt, MT, UW>;
-  static bool configured[64] = {false};  // per device, per kernel instantiation
-  static std::mutex once;
-  {
-    std::lock_guard<std::mutex> g(once);
-    if (!configured[ctx->device & 63]) {
-      ISHI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          std::min(kSmemBudget, ctx->smem_optin)));
-      configured[ctx->device & 63] = true;
-    }
-  }
-  const int grid = pl.Gc * pl.S;
-  const int block = (pl.W + 1) * 32;
-  kern<<<grid, block, pl.smem, st>>>(args);
+void free_workspace(Workspace *ws) {
+  if (ws->scratch) cudaFree(ws->scratch);
+  if (ws->counters) cudaFree(ws->counters);
+  if (ws->tiles) cudaFree(ws->tiles);
+  *ws = Workspace();
+}
+
+ishi_status tile_weight(ishi_ctx *ctx, const RowPlan &pl, long long n, uint8_t *dst, cudaStream_t st) {
+  const long long triples = (long long)pl.P * pl.units * kRowPanel;
+  const int grid = (int)std::min<long long>((triples + 255) / 256, (long long)ctx->sm_count * 16);
+  prepare_tiles_kernel<<<grid, 256, 0, st>>>(pl.src[0], pl.src[1], pl.src[2], pl.src[3], pl.nsec, n, pl.units,
+                                             pl.tile_bytes, dst);
   ISHI_CUDA(ctx, cudaGetLastError());
   return ISHI_OK;
 }
@@ -229,13 +270,13 @@ ishi_status launch_stream(ishi_ctx *ctx, const Plan &pl, const StreamArgs &args,
 template <class Fmt>
 ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
   auto kern = rowstream_kernel<Fmt>;
-  static bool configured[64] = {false};
+  static bool configured[64] = {false};  // per device, per kernel instantiation
   static std::mutex once;
   {
     std::lock_guard<std::mutex> g(once);
     if (!configured[ctx->device & 63]) {
       ISHI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (std::min(kSmemBudget, ctx->smem_optin) - 2048) / 2));
+                                          (std::min(kSmemPerSm, ctx->smem_optin) - 4096) / 2));
       configured[ctx->device & 63] = true;
     }
   }
@@ -244,75 +285,27 @@ ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cu
   return ISHI_OK;
 }
 
-struct GgmlCall {
-  const void *x;
-  int rows;
-  const void *blocks;
-  int type;
-  long long n, k;
-  void *y;
-  long long ldy;
-  int flags;
-};
-
-ishi_status run_ggml_mma(ishi_ctx *ctx, const Plan &pl, Workspace *ws, const GgmlCall &c,
-                         cudaStream_t st) {
-  StreamArgs a;
-  memset(&a, 0, sizeof(a));
-  const int ts = type_size(c.type);
-  a.src[0].base = static_cast<const uint8_t *>(c.blocks);
-  a.src[0].row_bytes = (long long)(c.k / 256) * ts;
-  a.src[0].unit_bytes = ts;
-  a.src[0].seg_off = 0;
-  a.nsrc = 1;
-  a.x = static_cast<const __half *>(c.x);
-  a.y = static_cast<__half *>(c.y);
-  a.ldy = c.ldy;
-  a.out_transposed = (c.flags & ISHI_OUT_TRANSPOSED) ? 1 : 0;
-  a.scratch = ws->scratch;
-  a.counters = ws->counters;
-  a.err = ctx->err_dev;
-  a.M = c.rows;
-  a.N = (int)c.n;
-  a.K = (int)c.k;
-  a.units = pl.units;
-  a.S = pl.S;
-  a.P = pl.P;
-  a.Gc = pl.Gc;
-  a.SL = pl.SL;
-  a.W = pl.W;
-  a.nstages = pl.nstages;
-  a.row_stride = pl.row_stride;
-  switch (c.type) {
-    case ISHI_GGML_Q4_K:
-      return pl.MT == 1 ? launch_stream<FmtQ4K, 1, 2>(ctx, pl, a, st)
-                        : launch_stream<FmtQ4K, 2, 1>(ctx, pl, a, st);
-    default:
-      return fail(ctx, ISHI_E_UNSUPPORTED, "no matmul kernel for GGML type %d", c.type);
-  }
-}
-
-ishi_status run_row(ishi_ctx *ctx, const RowPlan &pl, Workspace *ws, const uint8_t *tiles, int fmt, const void *x,
-                    int rows, long long n, long long k, void *y, long long ldy, int flags, int group_size,
-                    int scale_dtype, cudaStream_t st) {
+// One launch: x [rows <= 8, k] against the tiled weight.
+ishi_status run_row(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int fmt, const ishi_weight_desc &d,
+                    const void *x, int rows, void *y, long long ldy, int flags, cudaStream_t st) {
   RowArgs a;
   memset(&a, 0, sizeof(a));
-  a.tiles = tiles;
+  a.tiles = ws.tiles;
   a.tile_bytes = pl.tile_bytes;
-  for (int i = 0; i < kMaxSrc; ++i) {
+  for (int i = 0; i < 4; ++i) {
     a.sec_off[i] = pl.sec_off[i];
-    a.unit_bytes[i] = pl.unit_bytes[i];
+    a.sec_bytes[i] = pl.sec_bytes[i];
   }
   a.x = static_cast<const __half *>(x);
   a.y = static_cast<__half *>(y);
   a.ldy = ldy;
   a.out_transposed = (flags & ISHI_OUT_TRANSPOSED) ? 1 : 0;
-  a.scratch = ws->scratch;
-  a.counters = ws->counters;
+  a.scratch = ws.scratch;
+  a.counters = ws.counters;
   a.err = ctx->err_dev;
   a.M = rows;
-  a.N = (int)n;
-  a.K = (int)k;
+  a.N = (int)d.n;
+  a.K = (int)d.k;
   a.units = pl.units;
   a.P = pl.P;
   a.SL = pl.SL;
@@ -320,38 +313,83 @@ ishi_status run_row(ishi_ctx *ctx, const RowPlan &pl, Workspace *ws, const uint8
   a.nstages = pl.nstages;
   a.x_off = pl.x_off;
   a.bmin_off = pl.bmin_off;
+  a.xs_off = pl.xs_off;
   a.stage_bytes = pl.stage_bytes;
-  a.group_size = group_size;
-  a.scale_dtype = scale_dtype;
+  a.group_size = d.group_size;
+  a.scale_dtype = d.scale_dtype;
+  a.bits = d.bits;
   switch (fmt) {
     case ISHI_GGML_Q4_K: return launch_row<RowQ4K>(ctx, pl, a, st);
-    default: return fail(ctx, ISHI_E_UNSUPPORTED, "no tcgen05 kernel for format %d", fmt);
+    case ISHI_GGML_Q6_K: return launch_row<RowQ6K>(ctx, pl, a, st);
+    case ISHI_GGML_IQ2_XS: return launch_row<RowIQ2XS>(ctx, pl, a, st);
+    case 102: return launch_row<RowAffine<2>>(ctx, pl, a, st);
+    case 104: return launch_row<RowAffine<4>>(ctx, pl, a, st);
+    case 108: return launch_row<RowAffine<8>>(ctx, pl, a, st);
+    default: return fail(ctx, ISHI_E_UNSUPPORTED, "no kernel for format %d", fmt);
   }
 }
 
-bool has_row_kernel(int fmt) { return fmt == ISHI_GGML_Q4_K; }
-
-ishi_status check_ggml_call(ishi_ctx *ctx, const GgmlCall &c, long long blocks_bytes, int max_rows) {
-  if (!ctx) return ISHI_E_INVALID;
-  if (!c.x || !c.blocks || !c.y) return fail(ctx, ISHI_E_INVALID, "null pointer");
-  if (!aligned16(c.x) || !aligned16(c.blocks)) return fail(ctx, ISHI_E_INVALID, "x and blocks must be 16-byte aligned");
-  const int ts = type_size(c.type);
-  if (ts == 0) return fail(ctx, ISHI_E_UNSUPPORTED, "GGML type %d has no decoder here", c.type);
-  if (c.rows < 1 || c.rows > max_rows) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...%d", c.rows, max_rows);
-  if (c.k <= 0 || c.k % 256 != 0) return fail(ctx, ISHI_E_SHAPE, "k %lld is not a whole number of 256-blocks", c.k);
-  if (c.n <= 0) return fail(ctx, ISHI_E_SHAPE, "n must be positive");
-  if (c.n > (1ll << 31) - 16 || c.k > (1ll << 30)) return fail(ctx, ISHI_E_SHAPE, "shape too large");
-  if (blocks_bytes < c.n * (c.k / 256) * ts) return fail(ctx, ISHI_E_SHAPE, "block buffer shorter than n * k/256 * type size");
+// rows 1...16: one launch for up to eight rows, two for more (the weight then streams twice).
+ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int fmt, const ishi_weight_desc &d,
+                     const void *x, int rows, void *y, long long ldy, int flags, cudaStream_t st) {
+  for (int r0 = 0; r0 < rows; r0 += 8) {
+    const int nr = std::min(8, rows - r0);
+    const __half *xs = static_cast<const __half *>(x) + (long long)r0 * d.k;
+    __half *ys = static_cast<__half *>(y) + ((flags & ISHI_OUT_TRANSPOSED) ? (long long)r0 : (long long)r0 * ldy);
+    ishi_status s = run_row(ctx, pl, ws, fmt, d, xs, nr, ys, ldy, flags, st);
+    if (s != ISHI_OK) return s;
+  }
   return ISHI_OK;
 }
 
-int unit_bytes_ggml(int type) { return type_size(type); }
+ishi_status check_io(ishi_ctx *ctx, const void *x, int rows, const void *y, int max_rows) {
+  if (!x || !y) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (!aligned16(x)) return fail(ctx, ISHI_E_INVALID, "x must be 16-byte aligned");
+  if (rows < 1 || rows > max_rows) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...%d", rows, max_rows);
+  return ISHI_OK;
+}
 
-int row_skew_for(int fmt) {
-  switch (fmt) {
-    case ISHI_GGML_Q4_K: return FmtQ4K::kRowSkew;
-    default: return 32;
-  }
+// Kernel-level product on a caller's raw weight: re-tiles it into the context's buffer, then runs.
+ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x, int rows, void *y, cudaStream_t st) {
+  int64_t wb = 0;
+  ishi_status s = check_desc(ctx, d, &wb);
+  if (s != ISHI_OK) return s;
+  std::lock_guard<std::mutex> g(ctx->lock);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  RowPlan pl;
+  if (!make_row_plan(ctx, d, &pl)) return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
+  s = ensure_workspace(ctx, &ctx->ws, pl.scratch_floats, pl.counters, pl.tiles_bytes);
+  if (s != ISHI_OK) return s;
+  s = tile_weight(ctx, pl, d.n, ctx->ws.tiles, st);
+  if (s != ISHI_OK) return s;
+  return run_rows(ctx, pl, ctx->ws, format_of(d), d, x, rows, y, d.n, 0, st);
+}
+
+ishi_status ggml_raw(ishi_ctx *ctx, const void *x, int rows, const void *blocks, int64_t blocks_bytes, int type,
+                     int64_t n, int64_t k, void *y, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  ishi_status s = check_io(ctx, x, rows, y, 16);
+  if (s != ISHI_OK) return s;
+  ishi_weight_desc d;
+  memset(&d, 0, sizeof(d));
+  d.kind = ISHI_KIND_GGML;
+  d.ggml_type = type;
+  d.n = n;
+  d.k = k;
+  d.weight_dev = blocks;
+  d.weight_bytes = blocks_bytes;
+  return raw_product(ctx, d, x, rows, y, static_cast<cudaStream_t>(stream));
+}
+
+ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void *y, int64_t ldy, int flags,
+                              cudaStream_t st) {
+  ishi_ctx *ctx = p->ctx;
+  ishi_status s = check_io(ctx, x, rows, y, 16);
+  if (s != ISHI_OK) return s;
+  const int64_t need_ld = (flags & ISHI_OUT_TRANSPOSED) ? rows : p->d.n;
+  if (ldy < need_ld) return fail(ctx, ISHI_E_SHAPE, "ldy %lld shorter than %lld", (long long)ldy, (long long)need_ld);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  return run_rows(ctx, p->plan, p->ws, p->fmt, p->d, x, rows, y, ldy, flags, st);
 }
 
 }  // namespace
@@ -410,8 +448,7 @@ ishi_status ishi_ctx_create(int device, ishi_ctx **out) {
 void ishi_ctx_destroy(ishi_ctx *ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
-  if (ctx->ws.scratch) cudaFree(ctx->ws.scratch);
-  if (ctx->ws.counters) cudaFree(ctx->ws.counters);
+  free_workspace(&ctx->ws);
   if (ctx->err_host) cudaFreeHost(ctx->err_host);
   if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
   if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
@@ -449,24 +486,25 @@ int ishi_reference_minimum_rows(int64_t bytes) {
 int ishi_ggml_block_size(int t) { return type_size(t) ? 256 : 0; }
 int ishi_ggml_type_size(int t) { return type_size(t); }
 
-ishi_status ishi_ggml_dequantize(ishi_ctx *ctx, int type, const void *blocks, int64_t n_blocks,
-                                 void *out, int out_dtype, void *stream) {
+ishi_status ishi_ggml_dequantize(ishi_ctx *ctx, int type, const void *blocks, int64_t n_blocks, void *out,
+                                 int out_dtype, void *stream) {
   if (!ctx) return ISHI_E_INVALID;
   if (!blocks || !out) return fail(ctx, ISHI_E_INVALID, "null pointer");
   if (type_size(type) == 0) return fail(ctx, ISHI_E_UNSUPPORTED, "GGML type %d has no decoder here", type);
   if (n_blocks < 0) return fail(ctx, ISHI_E_SHAPE, "negative block count");
   if (n_blocks == 0) return ISHI_OK;
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int threads = 256;
   const long long want = (n_blocks * 32 + threads - 1) / threads;
   const int grid = (int)std::min<long long>(want, (long long)ctx->sm_count * 32);
   const uint8_t *b = static_cast<const uint8_t *>(blocks);
 #define ISHI_DQ(T, OT) ggml_dequantize_kernel<T, OT><<<grid, threads, 0, st>>>(b, n_blocks, static_cast<OT *>(out))
-#define ISHI_DQ_T(T)                                                   \
-  switch (out_dtype) {                                                 \
-    case ISHI_DT_F32: ISHI_DQ(T, float); break;                        \
-    case ISHI_DT_F16: ISHI_DQ(T, __half); break;                       \
-    case ISHI_DT_BF16: ISHI_DQ(T, __nv_bfloat16); break;               \
+#define ISHI_DQ_T(T)                                                             \
+  switch (out_dtype) {                                                           \
+    case ISHI_DT_F32: ISHI_DQ(T, float); break;                                  \
+    case ISHI_DT_F16: ISHI_DQ(T, __half); break;                                 \
+    case ISHI_DT_BF16: ISHI_DQ(T, __nv_bfloat16); break;                         \
     default: return fail(ctx, ISHI_E_INVALID, "bad output dtype %d", out_dtype); \
   }
   switch (type) {
@@ -481,14 +519,15 @@ ishi_status ishi_ggml_dequantize(ishi_ctx *ctx, int type, const void *blocks, in
 }
 
 ishi_status ishi_affine_dequantize(ishi_ctx *ctx, const void *w, const void *scales, const void *biases,
-                                   int scale_dtype, int group_size, int bits, int64_t n, int64_t k,
-                                   float *out, void *stream) {
+                                   int scale_dtype, int group_size, int bits, int64_t n, int64_t k, float *out,
+                                   void *stream) {
   if (!ctx) return ISHI_E_INVALID;
   if (!w || !scales || !biases || !out) return fail(ctx, ISHI_E_INVALID, "null pointer");
   if (bits < 2 || bits > 8) return fail(ctx, ISHI_E_SHAPE, "bits %d outside 2...8", bits);
   if (scale_dtype < ISHI_DT_F16 || scale_dtype > ISHI_DT_F32) return fail(ctx, ISHI_E_INVALID, "bad scale dtype");
   if (group_size <= 0 || k <= 0 || n <= 0 || k % group_size != 0 || (k * bits) % 32 != 0)
     return fail(ctx, ISHI_E_SHAPE, "k %lld does not fit groups of %d at %d bits", (long long)k, group_size, bits);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   const long long total = n * k;
   const int grid = (int)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
   affine_dequantize_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -507,6 +546,7 @@ ishi_status ishi_hadamard_rotate(ishi_ctx *ctx, const void *x, int64_t rows, int
     return fail(ctx, ISHI_E_SHAPE, "Hadamard block %d does not divide activation width %lld", block, (long long)width);
   const long long grid = rows * (width / block);
   if (grid > 0x7fffffffll) return fail(ctx, ISHI_E_SHAPE, "too many blocks");
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   const int threads = std::max(32, std::min(256, block / 2));
   hadamard_rotate_kernel<<<(int)grid, threads, block * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half *>(x), width, block, signs, static_cast<__half *>(y));
@@ -514,175 +554,74 @@ ishi_status ishi_hadamard_rotate(ishi_ctx *ctx, const void *x, int64_t rows, int
   return ISHI_OK;
 }
 
-ishi_status ishi_ggml_matmul_few(ishi_ctx *ctx, const void *x, int rows, const void *blocks,
-                                 int64_t blocks_bytes, int type, int64_t n, int64_t k, void *y,
-                                 void *stream) {
-  GgmlCall c{x, rows, blocks, type, n, k, y, n, 0};
-  ishi_status s = check_ggml_call(ctx, c, blocks_bytes, 16);
+ishi_status ishi_ggml_matmul_few(ishi_ctx *ctx, const void *x, int rows, const void *blocks, int64_t blocks_bytes,
+                                 int type, int64_t n, int64_t k, void *y, void *stream) {
+  return ggml_raw(ctx, x, rows, blocks, blocks_bytes, type, n, k, y, stream);
+}
+
+ishi_status ishi_ggml_matvec(ishi_ctx *ctx, const void *x, int rows, const void *blocks, int64_t blocks_bytes,
+                             int type, int64_t n, int64_t k, void *y, void *stream) {
+  return ggml_raw(ctx, x, rows, blocks, blocks_bytes, type, n, k, y, stream);
+}
+
+ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x, int rows, const void *w, const void *scales,
+                               const void *biases, int scale_dtype, int group_size, int bits, int64_t n, int64_t k,
+                               int route, void *y, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  (void)route;
+  ishi_status s = check_io(ctx, x, rows, y, 16);
   if (s != ISHI_OK) return s;
-  std::lock_guard<std::mutex> g(ctx->lock);
-  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
-  Plan pl;
-  int ub = unit_bytes_ggml(type);
-  if (!make_plan(ctx, type, n, k, rows, 1, &ub, row_skew_for(type), &pl))
-    return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)k);
-  s = ensure_workspace(ctx, &ctx->ws, pl.scratch_floats, (size_t)pl.P);
-  if (s != ISHI_OK) return s;
-  return run_ggml_mma(ctx, pl, &ctx->ws, c, static_cast<cudaStream_t>(stream));
-}
-
-// ---- projection -------------------------------------------------------------------------------
-
-struct ishi_projection_impl;
-
-ishi_status ishi_ggml_matvec(ishi_ctx *ctx, const void *x, int rows, const void *blocks,
-                             int64_t blocks_bytes, int type, int64_t n, int64_t k, void *y,
-                             void *stream) {
-  (void)x; (void)rows; (void)blocks; (void)blocks_bytes; (void)type; (void)n; (void)k; (void)y; (void)stream;
-  return fail(ctx, ISHI_E_UNSUPPORTED, "matvec kernel not built yet");
-}
-
-ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *, int, const void *, const void *, const void *,
-                               int, int, int, int64_t, int64_t, int, void *, void *) {
-  return fail(ctx, ISHI_E_UNSUPPORTED, "affine kernel not built yet");
-}
-
-}  // extern "C"
-
-// ---- projection: the PackedLinear counterpart -----------------------------------------------
-
-struct ishi_projection {
-  ishi_ctx *ctx = nullptr;
   ishi_weight_desc d;
-  Plan plan[2];       // warp-level kernel: rows 1..8 and rows 9..16
-  RowPlan row;        // tcgen05 kernel: rows 1..8
-  uint8_t *tiles = nullptr;  // the weight re-tiled for the tcgen05 kernel (library-owned)
-  int fmt = 0;
-  Workspace ws;       // this projection's own scratch, so apply never allocates
-  __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
-  int64_t weight_bytes = 0;
-};
-
-namespace {
-
-ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void *y, int64_t ldy,
-                              int flags, cudaStream_t st) {
-  ishi_ctx *ctx = p->ctx;
-  if (!x || !y) return fail(ctx, ISHI_E_INVALID, "null pointer");
-  if (!aligned16(x)) return fail(ctx, ISHI_E_INVALID, "x must be 16-byte aligned");
-  if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
-  const int64_t need_ld = (flags & ISHI_OUT_TRANSPOSED) ? rows : p->d.n;
-  if (ldy < need_ld) return fail(ctx, ISHI_E_SHAPE, "ldy %lld shorter than %lld", (long long)ldy, (long long)need_ld);
-  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
-  const Plan &pl = p->plan[rows > 8 ? 1 : 0];
-  if (p->d.kind == ISHI_KIND_GGML) {
-    GgmlCall c{x, rows, p->d.weight_dev, p->d.ggml_type, p->d.n, p->d.k, y, ldy, flags};
-    if (rows <= 8 && p->row.ok && ctx->route != ISHI_ROUTE_GEMV)
-      return run_row(ctx, p->row, &p->ws, p->tiles, p->fmt, x, rows, p->d.n, p->d.k, y, ldy, flags, 0, 0, st);
-    return run_ggml_mma(ctx, pl, &p->ws, c, st);
-  }
-  return fail(ctx, ISHI_E_UNSUPPORTED, "affine kernel not built yet");
+  memset(&d, 0, sizeof(d));
+  d.kind = ISHI_KIND_AFFINE;
+  d.bits = bits;
+  d.group_size = group_size;
+  d.scale_dtype = scale_dtype;
+  d.n = n;
+  d.k = k;
+  d.weight_dev = w;
+  d.weight_bytes = (bits >= 2 && bits <= 8 && n > 0 && k > 0) ? n * k * bits / 8 : 0;
+  d.scales_dev = scales;
+  d.biases_dev = biases;
+  return raw_product(ctx, d, x, rows, y, static_cast<cudaStream_t>(stream));
 }
 
-}  // namespace
-
-extern "C" {
+// ---- projection: the PackedLinear counterpart ---------------------------------------------------
 
 ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, ishi_projection **out) {
   if (!ctx || !out) return ISHI_E_INVALID;
   *out = nullptr;
   if (!desc) return fail(ctx, ISHI_E_INVALID, "null descriptor");
-  const ishi_weight_desc &d = *desc;
-  if (!d.weight_dev || !aligned16(d.weight_dev)) return fail(ctx, ISHI_E_INVALID, "weight pointer null or not 16-byte aligned");
-  if (d.n <= 0 || d.k <= 0) return fail(ctx, ISHI_E_SHAPE, "n and k must be positive");
-  if (d.n > (1ll << 31) - 16 || d.k > (1ll << 30)) return fail(ctx, ISHI_E_SHAPE, "shape too large");
-  if (d.k % 256 != 0) return fail(ctx, ISHI_E_SHAPE, "k %lld is not a multiple of 256", (long long)d.k);
-  if (d.hadamard_block != 0) {
-    const int b = d.hadamard_block;
-    if (b < 0 || (b & (b - 1)) != 0 || b > 8192 || d.k % b != 0)
-      return fail(ctx, ISHI_E_SHAPE, "Hadamard block %d does not divide input width %lld", b, (long long)d.k);
-  }
-  int nsrc = 0, unit_bytes[kMaxSrc] = {0, 0, 0}, fmt = 0;
-  int64_t bytes = 0;
-  if (d.kind == ISHI_KIND_GGML) {
-    const int ts = type_size(d.ggml_type);
-    if (ts == 0) return fail(ctx, ISHI_E_UNSUPPORTED, "GGML type %d has no decoder here", d.ggml_type);
-    bytes = d.n * (d.k / 256) * ts;
-    nsrc = 1;
-    unit_bytes[0] = ts;
-    fmt = d.ggml_type;
-  } else if (d.kind == ISHI_KIND_AFFINE) {
-    if (d.bits != 2 && d.bits != 4 && d.bits != 8) return fail(ctx, ISHI_E_UNSUPPORTED, "affine width %d has no kernel here", d.bits);
-    if (d.group_size != 32 && d.group_size != 64 && d.group_size != 128) return fail(ctx, ISHI_E_SHAPE, "group size %d outside {32, 64, 128}", d.group_size);
-    if (d.scale_dtype < ISHI_DT_F16 || d.scale_dtype > ISHI_DT_F32) return fail(ctx, ISHI_E_INVALID, "bad scale dtype");
-    if (!d.scales_dev || !d.biases_dev || !aligned16(d.scales_dev) || !aligned16(d.biases_dev))
-      return fail(ctx, ISHI_E_INVALID, "scales/biases null or not 16-byte aligned");
-    const int sb = d.scale_dtype == ISHI_DT_F32 ? 4 : 2;
-    bytes = d.n * d.k * d.bits / 8;
-    nsrc = 3;
-    unit_bytes[0] = 256 * d.bits / 8;
-    unit_bytes[1] = unit_bytes[2] = 256 / d.group_size * sb;
-    fmt = 100 + d.bits;
-  } else {
-    return fail(ctx, ISHI_E_INVALID, "bad weight kind %d", d.kind);
-  }
-  if (d.weight_bytes < bytes) return fail(ctx, ISHI_E_SHAPE, "weight buffer holds %lld bytes, shape needs %lld", (long long)d.weight_bytes, (long long)bytes);
-
+  int64_t wb = 0;
+  ishi_status s = check_desc(ctx, *desc, &wb);
+  if (s != ISHI_OK) return s;
   std::lock_guard<std::mutex> g(ctx->lock);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   ishi_projection *p = new (std::nothrow) ishi_projection();
   if (!p) return fail(ctx, ISHI_E_NOMEM, "out of host memory");
   p->ctx = ctx;
-  p->d = d;
-  p->weight_bytes = bytes;
-  if (d.kind == ISHI_KIND_AFFINE) {
-    const int sb = d.scale_dtype == ISHI_DT_F32 ? 4 : 2;
-    p->weight_bytes += 2 * d.n * (d.k / d.group_size) * sb;
+  p->d = *desc;
+  p->fmt = format_of(*desc);
+  p->weight_bytes = wb;
+  if (!make_row_plan(ctx, p->d, &p->plan)) {
+    delete p;
+    return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)desc->k);
   }
-  size_t floats = 0;
-  for (int i = 0; i < 2; ++i) {
-    if (!make_plan(ctx, fmt, d.n, d.k, i ? 16 : 8, nsrc, unit_bytes, row_skew_for(fmt), &p->plan[i])) {
-      delete p;
-      return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)d.k);
-    }
-    floats = std::max(floats, p->plan[i].scratch_floats);
+  s = ensure_workspace(ctx, &p->ws, p->plan.scratch_floats, p->plan.counters, p->plan.tiles_bytes);
+  // Re-tile the weight once; the caller's buffer is not read again afterwards.
+  if (s == ISHI_OK) s = tile_weight(ctx, p->plan, p->d.n, p->ws.tiles, 0);
+  if (s == ISHI_OK) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "tiling the weight: %s", cudaGetErrorString(e));
   }
-  size_t counters = (size_t)p->plan[0].P;
-  p->fmt = fmt;
-  if (has_row_kernel(fmt) && make_row_plan(ctx, d.n, d.k, nsrc, unit_bytes, &p->row)) {
-    floats = std::max(floats, p->row.scratch_floats);
-    counters = std::max(counters, p->row.counters);
-  }
-  ishi_status s = ensure_workspace(ctx, &p->ws, floats, counters);
-  if (s == ISHI_OK && p->row.ok) {
-    // re-tile the weight once; the caller's buffer stays as it is and is still used for 9...16 rows
-    cudaError_t e = cudaMalloc(&p->tiles, p->row.tiles_bytes);
-    if (e != cudaSuccess) {
-      s = fail(ctx, ISHI_E_CUDA, "cudaMalloc(tiled weight, %zu bytes): %s", p->row.tiles_bytes, cudaGetErrorString(e));
-    } else {
-      TileSrc ts[kMaxSrc];
-      memset(ts, 0, sizeof(ts));
-      const void *bases[kMaxSrc] = {d.weight_dev, d.scales_dev, d.biases_dev};
-      for (int i = 0; i < nsrc; ++i) {
-        ts[i].base = static_cast<const uint8_t *>(bases[i]);
-        ts[i].unit_bytes = unit_bytes[i];
-        ts[i].row_bytes = (long long)(d.k / 256) * unit_bytes[i];
-        ts[i].sec_off = p->row.sec_off[i];
-      }
-      const long long triples = (long long)p->row.P * p->row.units * kRowPanel;
-      const int grid = (int)std::min<long long>((triples + 255) / 256, (long long)ctx->sm_count * 16);
-      prepare_tiles_kernel<<<grid, 256>>>(ts[0], ts[1], ts[2], nsrc, d.n, p->row.units, p->row.tile_bytes, p->tiles);
-      e = cudaGetLastError();
-      if (e == cudaSuccess) e = cudaDeviceSynchronize();
-      if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "tiling the weight: %s", cudaGetErrorString(e));
-    }
-  }
-  if (s == ISHI_OK && d.hadamard_block != 0) {
-    cudaError_t e = cudaMalloc(&p->xr, (size_t)16 * d.k * sizeof(__half));
+  if (s == ISHI_OK && p->d.hadamard_block != 0) {
+    cudaError_t e = cudaMalloc(&p->xr, (size_t)16 * p->d.k * sizeof(__half));
     if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "cudaMalloc(rotated x): %s", cudaGetErrorString(e));
   }
   if (s != ISHI_OK) {
-    ishi_projection_destroy(p);
+    free_workspace(&p->ws);
+    if (p->xr) cudaFree(p->xr);
+    delete p;
     return s;
   }
   *out = p;
@@ -692,10 +631,8 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
 void ishi_projection_destroy(ishi_projection *p) {
   if (!p) return;
   cudaSetDevice(p->ctx->device);
-  if (p->ws.scratch) cudaFree(p->ws.scratch);
-  if (p->ws.counters) cudaFree(p->ws.counters);
+  free_workspace(&p->ws);
   if (p->xr) cudaFree(p->xr);
-  if (p->tiles) cudaFree(p->tiles);
   delete p;
 }
 

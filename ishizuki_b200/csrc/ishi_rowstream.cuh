@@ -46,8 +46,8 @@ constexpr uint32_t kColA0 = 0, kColA1 = 64, kColD = 128, kColAmin = 192, kColDmi
 struct RowArgs {
   const uint8_t *tiles;  // [P][units][tile_bytes]: see prepare_tiles_kernel
   int tile_bytes;        // 128 rows x bytes of one unit, all byte streams of the format
-  int sec_off[kMaxSrc];  // offset of each byte stream's 128-row section inside a tile
-  int unit_bytes[kMaxSrc];
+  int sec_off[4];        // offset of each section (128 rows x field bytes) inside a tile
+  int sec_bytes[4];      // bytes per row of each section
   const __half *x;
   __half *y;
   long long ldy;
@@ -62,9 +62,10 @@ struct RowArgs {
   int kc;          // units per stage
   int nstages;
   int x_off;       // offset of the activation chunk inside a stage
-  int bmin_off;    // offset of the group-sum operand inside a stage
+  int bmin_off;    // offset of the group-sum MMA operand inside a stage (formats with a minimum term)
+  int xs_off;      // offset of the fp32 group sums of x inside a stage (affine packs: bias term)
   int stage_bytes;
-  int group_size, scale_dtype;
+  int group_size, scale_dtype, bits;
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
@@ -166,7 +167,8 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
   uint64_t *a_ready = empty + nst;                      // 4 decode warps: A stored, D of the step before read
   uint64_t *mma_done = a_ready + 1;                     // tensor core's commit for a step
   const uint32_t bars_bytes = 128;
-  uint8_t *stage0 = smem + bars_bytes;
+  uint8_t *table = smem + bars_bytes;  // format's lookup table, if it has one
+  uint8_t *stage0 = table + Fmt::kTableBytes;
   const uint32_t stage0_u32 = smem_u32(stage0);
 
   if (threadIdx.x == 0) {
@@ -180,8 +182,9 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(&s_tmem, kTmemCols);
+  Fmt::build_table(table, threadIdx.x, blockDim.x);
   // the second 16-byte core matrix of every group-sum operand stays zero for the whole kernel
-  for (int i = threadIdx.x; i < nst * a.kc * 2 * 64; i += blockDim.x) {
+  for (int i = threadIdx.x; Fmt::kHasMin && i < nst * a.kc * 2 * 64; i += blockDim.x) {
     const int st = i / (a.kc * 2 * 64), rem = i % (a.kc * 2 * 64);
     reinterpret_cast<uint32_t *>(stage0 + (size_t)st * a.stage_bytes + a.bmin_off)[rem] = 0u;
   }
@@ -232,7 +235,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
     while (ok && walk.next(p, u0, nu, last)) {
       const int s = it % nst;
       const uint32_t ph = (uint32_t)(it / nst) & 1u;
-      uint4 xv[Fmt::kXRegs];
+      typename Fmt::XRegs xv;
       Fmt::load_x(a, u0, nu, lane, xv);  // in flight while the stage drains
       if (it >= nst) ok = mbar_wait(&empty[s], ph ^ 1u, abort_word);
       if (!ok) break;
@@ -260,7 +263,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
         tc_fence_after();
         if (lane == 0) {
           const uint32_t acol = tmem + ((H & 1u) ? kColA1 : kColA0);
-          Fmt::issue_step(tmem, acol, xbase + (uint32_t)hs * 2048u, mbase + (uint32_t)hs * 256u, hs & 1);
+          Fmt::issue_step(a, tmem, acol, xbase + (uint32_t)hs * 2048u, mbase + (uint32_t)hs * 256u, hs & 1);
           umma_commit(mma_done);
           if (hs == 2 * nu - 1) umma_commit(&empty[s]);
         }
@@ -273,6 +276,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
     const int r = threadIdx.x;  // row inside the panel; also this thread's tensor-memory lane
     const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
     typename Fmt::RowState rs;
+    Fmt::init_state(rs, smem_u32(table));
     float acc[8];
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m] = 0.f;
@@ -281,6 +285,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
     bool pending = false;  // accumulators of step H-1 not yet read back
     bool ok = true;
     int first_unit_of_panel = -1;
+    int release_s = -1;  // a stage is handed back only after the sums of its last step were used
     while (ok && walk.next(p, u0, nu, last)) {
       const int s = it % nst;
       const uint32_t ph = (uint32_t)(it / nst) & 1u;
@@ -299,20 +304,24 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
             ok = mbar_wait(mma_done, (H - 1u) & 1u, abort_word);
             if (!ok) break;
             tc_fence_after();
-            Fmt::consume_step(rs, acc, tlane);
+            Fmt::consume_step(rs, a, acc, tlane);
+            if (release_s >= 0) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&empty[release_s]);
+              release_s = -1;
+            }
           }
           Fmt::store_min(rs, hh, tlane);
           tc_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(a_ready);
-          Fmt::advance(rs, hh);
+          Fmt::advance(rs, hh, stage + a.xs_off + (uint32_t)(2 * ul + hh) * 128u);
           pending = true;
         }
       }
       if (!ok) break;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
+      release_s = s;
       ++it;
 
       if (last) {
@@ -320,14 +329,17 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
         ok = mbar_wait(mma_done, (H - 1u) & 1u, abort_word);
         if (!ok) break;
         tc_fence_after();
-        Fmt::consume_step(rs, acc, tlane);
+        Fmt::consume_step(rs, a, acc, tlane);
         pending = false;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[release_s]);
+        release_s = -1;
 
         const bool whole = first_unit_of_panel == 0 && u0 + nu == a.units;
         bool write_out = true;
         if (!whole) {
           long long jf;
-          const int cnt = panel_touch(p, 0, a.units, 1, a.P, (int)gridDim.x, &jf);
+          const int cnt = panel_touch(p, a.units, a.P, (int)gridDim.x, &jf);
           const int slot = jf < 0 ? first_unit_of_panel : (int)(blockIdx.x - jf);
           float *sl = a.scratch + (((long long)p * a.SL + slot) * 8) * kRowPanel + r;
 #pragma unroll
@@ -365,6 +377,10 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
         first_unit_of_panel = -1;
       }
     }
+    if (ok && release_s >= 0) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[release_s]);
+    }
   }
 
   tc_fence_before();
@@ -374,20 +390,25 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
   if (threadIdx.x == 0 && s_abort != 0) atomicExch(a.err, 1);
 }
 
-// One-time re-tiling of a weight for rowstream_kernel. Source: up to three row-major byte streams
-// (GGUF blocks, or an affine pack's codes, scales and biases), stream i holding unit_bytes[i]
-// bytes per row per unit. Destination: [panel][unit][stream][row in panel][unit_bytes[i]], rows
-// past N zero. Streams whose rows are only 2-byte aligned are copied 2 bytes at a time.
+// One-time re-tiling of a weight for rowstream_kernel. A tile holds the 128 row blocks of one
+// (panel, unit) pair, split into up to four sections, each the same field of all 128 rows back to
+// back: [panel][unit][section][row in panel][field bytes]. A section is described by where the
+// field starts in the source, the distance between rows and between units there, and its length
+// (e.g. Q6_K: ql, qh, scales, d out of one 210-byte block; an affine pack: codes, scales and
+// biases out of three arrays). Rows past N are zero. Fields are 2-byte aligned at worst, so the
+// copy moves 2 bytes at a time.
 struct TileSrc {
-  const uint8_t *base;
-  long long row_bytes;
-  int unit_bytes;
-  int sec_off;
+  const uint8_t *base;   // field of row 0, unit 0
+  long long row_bytes;   // source distance between rows
+  int unit_stride;       // source distance between units of a row
+  int field_bytes;       // bytes per row per unit
+  int sec_off;           // section offset inside a tile
 };
 
-__global__ void __launch_bounds__(256) prepare_tiles_kernel(TileSrc s0, TileSrc s1, TileSrc s2, int nsrc, long long N,
-                                                            int units, int tile_bytes, uint8_t *__restrict__ dst) {
-  const TileSrc src[3] = {s0, s1, s2};
+__global__ void __launch_bounds__(256) prepare_tiles_kernel(TileSrc s0, TileSrc s1, TileSrc s2, TileSrc s3, int nsec,
+                                                            long long N, int units, int tile_bytes,
+                                                            uint8_t *__restrict__ dst) {
+  const TileSrc src[4] = {s0, s1, s2, s3};
   const long long P = (N + kRowPanel - 1) / kRowPanel;
   const long long total = P * units * kRowPanel;  // (panel, unit, row) triples
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -398,12 +419,12 @@ __global__ void __launch_bounds__(256) prepare_tiles_kernel(TileSrc s0, TileSrc 
     const long long p = pu / units;
     const long long row = p * kRowPanel + r;
     uint8_t *tile = dst + pu * (long long)tile_bytes;
-    for (int k = 0; k < nsrc; ++k) {
-      uint16_t *o = reinterpret_cast<uint16_t *>(tile + src[k].sec_off + (long long)r * src[k].unit_bytes);
-      const int n16 = src[k].unit_bytes / 2;
+    for (int k = 0; k < nsec; ++k) {
+      uint16_t *o = reinterpret_cast<uint16_t *>(tile + src[k].sec_off + (long long)r * src[k].field_bytes);
+      const int n16 = src[k].field_bytes / 2;
       if (row < N) {
         const uint16_t *in = reinterpret_cast<const uint16_t *>(src[k].base + row * src[k].row_bytes +
-                                                                (long long)u * src[k].unit_bytes);
+                                                                (long long)u * src[k].unit_stride);
         for (int j = 0; j < n16; ++j) o[j] = in[j];
       } else {
         for (int j = 0; j < n16; ++j) o[j] = 0;

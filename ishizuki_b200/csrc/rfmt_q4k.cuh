@@ -21,6 +21,9 @@ namespace ishi {
 
 struct RowQ4K {
   static constexpr int kUnitBytes = 144;
+  static constexpr bool kHasMin = true;
+  static constexpr int kTableBytes = 0;
+  static __device__ __forceinline__ void build_table(uint8_t *, int, int) {}
 
   struct RowState {
     float d, nmin;        // block scale, dmin * 2^24
@@ -29,6 +32,8 @@ struct RowQ4K {
     float ps[4], pmin;    // ... of the step whose accumulators are still in tensor memory
     int prev_hh;
   };
+
+  static __device__ __forceinline__ void init_state(RowState &, uint32_t) {}
 
   template <int E>
   static __device__ __forceinline__ float byte_scaled(uint32_t packed, int i) {
@@ -82,14 +87,17 @@ struct RowQ4K {
     tmem_st8(tlane + kColAmin, r);
   }
 
-  static __device__ __forceinline__ void advance(RowState &rs, int hh) {
+  static __device__ __forceinline__ void advance(RowState &rs, int hh, uint32_t xs_addr) {
+    (void)xs_addr;
 #pragma unroll
     for (int i = 0; i < 4; ++i) rs.ps[i] = rs.cs[i];
     rs.pmin = rs.nmin;
     rs.prev_hh = hh;
   }
 
-  static __device__ __forceinline__ void consume_step(const RowState &rs, float (&acc)[8], uint32_t tlane) {
+  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &a, float (&acc)[8],
+                                                      uint32_t tlane) {
+    (void)a;
     float dg[4][8], dm[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) tmem_ld8(tlane + kColD + 16u * i, dg[i]);
@@ -106,8 +114,9 @@ struct RowQ4K {
   }
 
   // one thread: the nine MMAs of a step
-  static __device__ __forceinline__ void issue_step(uint32_t tmem, uint32_t acol, uint32_t xaddr, uint32_t maddr,
-                                                    int hh) {
+  static __device__ __forceinline__ void issue_step(const RowArgs &a, uint32_t tmem, uint32_t acol, uint32_t xaddr,
+                                                    uint32_t maddr, int hh) {
+    (void)a;
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -121,7 +130,11 @@ struct RowQ4K {
   // gq = lane / 8) takes eight consecutive k of row m per sub-block, so every load is issued
   // before the warp waits for the stage to be free.
   static constexpr int kXRegs = 16;  // sub-blocks per stage at most (two units)
-  static __device__ __forceinline__ void load_x(const RowArgs &a, int u0, int nu, int lane, uint4 (&v)[kXRegs]) {
+  struct XRegs {
+    uint4 v[kXRegs];
+  };
+  static __device__ __forceinline__ void load_x(const RowArgs &a, int u0, int nu, int lane, XRegs &xr_) {
+    uint4(&v)[kXRegs] = xr_.v;
     const int m = lane & 7, gq = lane >> 3;
     const bool live = m < a.M;
     const __half *xr = a.x + (long long)(live ? m : 0) * a.K + (long long)u0 * 256 + 8 * gq;
@@ -135,7 +148,8 @@ struct RowQ4K {
   // second half: core matrices (k order 0,2,1,3 inside every four) and the per-sub-block sums,
   // split into an fp16 high and low part, into the group-sum operand
   static __device__ __forceinline__ void store_x(const RowArgs &a, uint32_t stage, int nu, int lane,
-                                                 const uint4 (&v)[kXRegs]) {
+                                                 const XRegs &xr_) {
+    const uint4(&v)[kXRegs] = xr_.v;
     const int m = lane & 7, gq = lane >> 3;
 #pragma unroll
     for (int sb = 0; sb < kXRegs; ++sb) {

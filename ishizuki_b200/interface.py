@@ -228,6 +228,7 @@ class VerifyMatmul:
         n = w.shape[0]
         if w.shape[1] * 32 != k * bits or scales.dtype != biases.dtype:
             return None
+        scales, biases = scales.contiguous(), biases.contiguous()
         y = torch.empty((m, n), dtype=torch.float16, device=x.device)
         rc = ctx.lib.ishi_verify_matmul(ctx.handle, _ptr(x), m, _ptr(w), _ptr(scales), _ptr(biases),
                                         _SCALE_DT[scales.dtype], groupSize, bits, n, k, route, _ptr(y),
