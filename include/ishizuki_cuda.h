@@ -37,7 +37,8 @@ enum {
   ISHI_E_UNSUPPORTED = 3, /* a format or width this library has no kernel for */
   ISHI_E_CUDA = 4,        /* a CUDA runtime call failed; see ishi_last_error */
   ISHI_E_TIMEOUT = 5,     /* a bounded device-side wait gave up; outputs of that call are invalid */
-  ISHI_E_NOMEM = 6
+  ISHI_E_NOMEM = 6,
+  ISHI_E_TOO_LARGE = 7    /* larger than the built-in scratch of ishi_q4k_matmul_few_static */
 };
 
 /* GGML block types, numbered as in GGUF (Sources/IshizukiKit/Config/GGUFFile.swift:13-44). */
@@ -157,6 +158,33 @@ int ishi_reference_minimum_rows(int64_t bytes);
 /* GGMLType.blockSize / typeSize (GGUFFile.swift:44-80); 0 for a type this library lacks. */
 int ishi_ggml_block_size(int ggml_type);
 int ishi_ggml_type_size(int ggml_type);
+
+/* ---- for callers that cannot allocate --------------------------------------------------------- */
+
+/* Has no counterpart in the reference. x [rows, k] against raw Q4_K blocks [n][k/256][144], like
+ * ishi_ggml_matmul_few, for a host that has no way to obtain device memory of its own beyond the
+ * buffers it is handed: a plugin running inside another runtime that reserved the whole GPU up
+ * front and hands out fixed input/output buffers, or a serving loop whose rules forbid allocation
+ * after start-up. Such a caller cannot create a context or a projection, since both allocate,
+ * so this entry point takes none: it works on the current device and everything the kernel needs
+ * besides x, the blocks and y (the re-tiled copy of the weight, the partial sums of panels shared
+ * between CTAs, their arrival counters, the error word) lives in one 16 MiB array that is part
+ * of the library image on every GPU that loads it. It calls no cudaMalloc, cudaFree or any other
+ * allocating routine.
+ *
+ * Limits: rows 1...16, k a multiple of 256, at most 131072 output rows, the weight at most
+ * 12 MiB of blocks (n * k/256 * 144 bytes, n rounded up to 128), and its partial-sum slots
+ * within about 3.9 MiB; anything larger returns ISHI_E_TOO_LARGE and launches nothing.
+ *
+ * The first call on a device looks up the array's device address and sets the kernel's
+ * shared-memory limit; make that first call outside any stream capture. The call returns when
+ * y is complete. All calls on a device share the one array and it keeps whatever the last call
+ * left in it: the counters and the error word are cleared at the start of every call, the rest is
+ * overwritten before it is read. Two calls that overlap on the same GPU (two host threads, two
+ * streams) race on it: serialise them. */
+ishi_status ishi_q4k_matmul_few_static(const void *x_dev, int rows, const void *blocks_dev,
+                                       int64_t blocks_bytes, int64_t n, int64_t k, void *y_dev,
+                                       void *stream);
 
 #ifdef __cplusplus
 }

@@ -8,7 +8,7 @@ from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 
 from . import build as _build
 
-OK, E_INVALID, E_SHAPE, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_NOMEM = range(7)
+OK, E_INVALID, E_SHAPE, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_NOMEM, E_TOO_LARGE = range(8)
 GGML_Q4_K, GGML_Q6_K, GGML_IQ2_XS = 12, 14, 17
 KIND_AFFINE, KIND_GGML = 0, 1
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
@@ -53,6 +53,7 @@ SIGNATURES = {
     "ishi_reference_minimum_rows": (c_int, [c_int64]),
     "ishi_ggml_block_size": (c_int, [c_int]),
     "ishi_ggml_type_size": (c_int, [c_int]),
+    "ishi_q4k_matmul_few_static": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
 }
 
 _lib = None

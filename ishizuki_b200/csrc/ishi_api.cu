@@ -407,6 +407,7 @@ const char *ishi_status_string(ishi_status s) {
     case ISHI_E_CUDA: return "CUDA error";
     case ISHI_E_TIMEOUT: return "device-side wait timed out";
     case ISHI_E_NOMEM: return "out of memory";
+    case ISHI_E_TOO_LARGE: return "larger than the built-in scratch of the no-allocation entry point";
     default: return "unknown status";
   }
 }
@@ -716,3 +717,84 @@ ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, i
 }
 
 }  // extern "C"
+
+// ---- the entry point for callers that cannot allocate ---------------------------------------------
+//
+// Everything rowstream_kernel needs beyond the caller's x, blocks and y sits in this one array,
+// which is part of the library image on every GPU that loads it:
+//   [0, 16 KiB)        arrival counters, one per (panel, warp): at most 1024 panels
+//   [16 KiB, 64 KiB)   the error word a bounded wait raises (first 4 bytes)
+//   [64 KiB, 4 MiB)    fp32 partial sums of panels shared between CTAs
+//   [4 MiB, 16 MiB)    the weight re-tiled for the kernel
+// On the host the symbol below is only a stand-in: its device address comes from
+// cudaGetSymbolAddress, once per device, and that address is what the kernels are given.
+namespace {
+constexpr size_t kStaticBytes = 16u << 20;
+constexpr size_t kStaticCounters = 0, kStaticCountersBytes = 16u << 10;
+constexpr size_t kStaticErr = 16u << 10;
+constexpr size_t kStaticPartials = 64u << 10, kStaticPartialsBytes = (4u << 20) - (64u << 10);
+constexpr size_t kStaticTiles = 4u << 20, kStaticTilesBytes = 12u << 20;
+}  // namespace
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+extern "C" ishi_status ishi_q4k_matmul_few_static(const void *x, int rows, const void *blocks, int64_t blocks_bytes,
+                                                  int64_t n, int64_t k, void *y, void *stream) {
+  static unsigned char *base[64] = {nullptr};  // device address of the array, per device
+  static std::mutex setup_lock;
+
+  ishi_ctx tmp;  // a stack record for the helpers; nothing in it owns memory
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ISHI_E_CUDA;
+  tmp.device = dev;
+  if (cudaDeviceGetAttribute(&tmp.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&tmp.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+    return ISHI_E_CUDA;
+
+  ishi_status s = check_io(&tmp, x, rows, y, 16);
+  if (s != ISHI_OK) return s;
+  ishi_weight_desc d;
+  memset(&d, 0, sizeof(d));
+  d.kind = ISHI_KIND_GGML;
+  d.ggml_type = ISHI_GGML_Q4_K;
+  d.n = n;
+  d.k = k;
+  d.weight_dev = blocks;
+  d.weight_bytes = blocks_bytes;
+  int64_t wb = 0;
+  s = check_desc(&tmp, d, &wb);
+  if (s != ISHI_OK) return s;
+  RowPlan pl;
+  if (!make_row_plan(&tmp, d, &pl)) return ISHI_E_SHAPE;
+  if (pl.counters * sizeof(unsigned int) > kStaticCountersBytes || pl.scratch_floats * sizeof(float) > kStaticPartialsBytes ||
+      pl.tiles_bytes > kStaticTilesBytes)
+    return ISHI_E_TOO_LARGE;
+
+  unsigned char *b = nullptr;
+  {
+    std::lock_guard<std::mutex> g(setup_lock);
+    if (base[dev] == nullptr) {
+      void *p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return ISHI_E_CUDA;
+      base[dev] = static_cast<unsigned char *>(p);
+    }
+    b = base[dev];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the counters must start at zero and the error word clear, whatever the last call left behind
+  if (cudaMemsetAsync(b + kStaticCounters, 0, kStaticCountersBytes + 64, st) != cudaSuccess) return ISHI_E_CUDA;
+
+  Workspace ws;
+  ws.counters = reinterpret_cast<unsigned int *>(b + kStaticCounters);
+  ws.scratch = reinterpret_cast<float *>(b + kStaticPartials);
+  ws.tiles = b + kStaticTiles;
+  tmp.err_dev = reinterpret_cast<int *>(b + kStaticErr);
+  s = tile_weight(&tmp, pl, n, ws.tiles, st);
+  if (s == ISHI_OK) s = run_rows(&tmp, pl, ws, ISHI_GGML_Q4_K, d, x, rows, y, n, 0, st);
+  ws = Workspace();  // nothing here was allocated, nothing to free
+  if (s != ISHI_OK) return s;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return ISHI_E_CUDA;
+  int raised = 0;
+  if (cudaMemcpy(&raised, b + kStaticErr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ISHI_E_CUDA;
+  return raised ? ISHI_E_TIMEOUT : ISHI_OK;
+}
