@@ -267,9 +267,9 @@ ishi_status tile_weight(ishi_ctx *ctx, const RowPlan &pl, long long n, uint8_t *
   return ISHI_OK;
 }
 
-template <class Fmt>
-ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
-  auto kern = rowstream_kernel<Fmt>;
+template <class Fmt, int MC>
+ishi_status launch_row_mc(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
+  auto kern = rowstream_kernel<Fmt, MC>;
   static bool configured[64] = {false};  // per device, per kernel instantiation
   static std::mutex once;
   {
@@ -283,6 +283,15 @@ ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cu
   kern<<<pl.grid, kRowThreads, pl.smem, st>>>(args);
   ISHI_CUDA(ctx, cudaGetLastError());
   return ISHI_OK;
+}
+
+// Picks the kernel instance that keeps as many accumulator columns as there are activation rows.
+template <class Fmt>
+ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
+  if (args.M <= 1) return launch_row_mc<Fmt, 1>(ctx, pl, args, st);
+  if (args.M <= 2) return launch_row_mc<Fmt, 2>(ctx, pl, args, st);
+  if (args.M <= 4) return launch_row_mc<Fmt, 4>(ctx, pl, args, st);
+  return launch_row_mc<Fmt, 8>(ctx, pl, args, st);
 }
 
 // One launch: x [rows <= 8, k] against the tiled weight.

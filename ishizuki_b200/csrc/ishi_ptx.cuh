@@ -30,6 +30,8 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
                : "memory");
 }
 
+// One poll: blocks for a short hardware-defined time while the phase is incomplete, returns at
+// once when it completes. (An explicit, longer suspend-time hint was measured slower here.)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -43,15 +45,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 
 // Every wait in these kernels is bounded: a phase that has not completed after kWaitSpins polls
-// (each poll itself blocks for a hardware-defined slice, so this is on the order of a second)
+// (each poll itself blocks for a hardware-defined slice, so the bound is on the order of a second)
 // makes the waiter raise the abort word and return false. Other waiters see the abort word and
 // give up at once, so a kernel whose producer or consumers went wrong drains instead of hanging.
 constexpr uint32_t kWaitSpins = 1u << 22;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word) {
+  if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kWaitSpins; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_word != 0) return false;
+    if (*abort_word != 0) return false;
   }
   *abort_word = 1;
   return false;

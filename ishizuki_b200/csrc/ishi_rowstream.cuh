@@ -103,14 +103,48 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&d)[8]) {
                : "memory");
 }
 
-// D[tmem_d] (+)= A[tmem_a] * B[desc]; M = 128, N = 16, K = 16, fp16 in, fp32 out.
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&d)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, float (&d)[2]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0,%1}, [%2];" : "=f"(d[0]), "=f"(d[1]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, float (&d)[1]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=f"(d[0]) : "r"(taddr) : "memory");
+}
+// the first MC accumulator columns of this thread's row
+template <int MC>
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, float (&d)[MC]);
+template <>
+__device__ __forceinline__ void tmem_ldn<8>(uint32_t taddr, float (&d)[8]) { tmem_ld8(taddr, d); }
+template <>
+__device__ __forceinline__ void tmem_ldn<4>(uint32_t taddr, float (&d)[4]) { tmem_ld4(taddr, d); }
+template <>
+__device__ __forceinline__ void tmem_ldn<2>(uint32_t taddr, float (&d)[2]) { tmem_ld2(taddr, d); }
+template <>
+__device__ __forceinline__ void tmem_ldn<1>(uint32_t taddr, float (&d)[1]) { tmem_ld1(taddr, d); }
+
+// D[tmem_d] (+)= A[tmem_a] * B[desc]; M = 128, N = 16, K = 16, fp16 in, fp32 out. The accumulate
+// flag is almost always a compile-time constant at the call site, so the two cases are separate
+// instructions with a constant predicate instead of a computed one.
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if (accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc)
+        : "memory");
+  }
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -152,7 +186,9 @@ struct RowWalk {
   }
 };
 
-template <class Fmt>
+// MC: accumulator columns read back and kept per row (the activation rows rounded up to 1, 2, 4
+// or 8); the MMAs always compute the full tile.
+template <class Fmt, int MC>
 __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_abort;
@@ -247,6 +283,9 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
     }
   } else if (warp == 6) {
     // ---------------- tensor core issue ----------------
+    // every operand of the MMA instruction has to sit in a uniform register; the tensor-memory
+    // base was read from shared memory, so a warp reduction tells the compiler it is uniform
+    const uint32_t tmem_u = __reduce_or_sync(0xffffffffu, tmem);
     int it = 0;
     uint32_t H = 0;
     bool ok = true;
@@ -262,8 +301,9 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t acol = tmem + ((H & 1u) ? kColA1 : kColA0);
-          Fmt::issue_step(a, tmem, acol, xbase + (uint32_t)hs * 2048u, mbase + (uint32_t)hs * 256u, hs & 1);
+          const uint32_t acol = tmem_u + ((H & 1u) ? kColA1 : kColA0);
+          Fmt::issue_step(a, tmem_u, acol, make_bdesc(xbase + (uint32_t)hs * 2048u, 0u),
+                          make_bdesc(mbase + (uint32_t)hs * 256u, 0u), hs & 1);
           umma_commit(mma_done);
           if (hs == 2 * nu - 1) umma_commit(&empty[s]);
         }
@@ -277,9 +317,9 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
     const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
     typename Fmt::RowState rs;
     Fmt::init_state(rs, smem_u32(table));
-    float acc[8];
+    float acc[MC];
 #pragma unroll
-    for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+    for (int m = 0; m < MC; ++m) acc[m] = 0.f;
     int it = 0;
     uint32_t H = 0;
     bool pending = false;  // accumulators of step H-1 not yet read back
@@ -304,7 +344,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
             ok = mbar_wait(mma_done, (H - 1u) & 1u, abort_word);
             if (!ok) break;
             tc_fence_after();
-            Fmt::consume_step(rs, a, acc, tlane);
+            Fmt::template consume_step<MC>(rs, a, acc, tlane);
             if (release_s >= 0) {
               __syncwarp();
               if (lane == 0) mbar_arrive(&empty[release_s]);
@@ -329,7 +369,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
         ok = mbar_wait(mma_done, (H - 1u) & 1u, abort_word);
         if (!ok) break;
         tc_fence_after();
-        Fmt::consume_step(rs, a, acc, tlane);
+        Fmt::template consume_step<MC>(rs, a, acc, tlane);
         pending = false;
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[release_s]);
@@ -343,7 +383,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
           const int slot = jf < 0 ? first_unit_of_panel : (int)(blockIdx.x - jf);
           float *sl = a.scratch + (((long long)p * a.SL + slot) * 8) * kRowPanel + r;
 #pragma unroll
-          for (int m = 0; m < 8; ++m) __stcg(sl + m * kRowPanel, acc[m]);
+          for (int m = 0; m < MC; ++m) __stcg(sl + m * kRowPanel, acc[m]);
           __threadfence();
           __syncwarp();
           unsigned int old = 0;
@@ -353,18 +393,18 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
           if (write_out) {
             __threadfence();
 #pragma unroll
-            for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+            for (int m = 0; m < MC; ++m) acc[m] = 0.f;
             for (int i = 0; i < cnt; ++i) {
               const float *s2 = a.scratch + (((long long)p * a.SL + i) * 8) * kRowPanel + r;
 #pragma unroll
-              for (int m = 0; m < 8; ++m) acc[m] += __ldcg(s2 + m * kRowPanel);
+              for (int m = 0; m < MC; ++m) acc[m] += __ldcg(s2 + m * kRowPanel);
             }
             if (lane == 0) a.counters[p * 4 + warp] = 0u;
           }
         }
         if (write_out && row < a.N) {
 #pragma unroll
-          for (int m = 0; m < 8; ++m) {
+          for (int m = 0; m < MC; ++m) {
             if (m < a.M) {
               const __half h = __float2half_rn(acc[m]);
               if (a.out_transposed) a.y[row * a.ldy + m] = h;
@@ -373,7 +413,7 @@ __global__ void __launch_bounds__(kRowThreads, 2) rowstream_kernel(const RowArgs
           }
         }
 #pragma unroll
-        for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+        for (int m = 0; m < MC; ++m) acc[m] = 0.f;
         first_unit_of_panel = -1;
       }
     }

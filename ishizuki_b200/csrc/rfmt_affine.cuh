@@ -133,13 +133,14 @@ struct RowAffine {
     rs.pxs = xs_addr;
   }
 
-  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &a, float (&acc)[8],
+  template <int MC>
+  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &a, float (&acc)[MC],
                                                       uint32_t tlane) {
     const int G = 128 / a.group_size;
-    float dg[4][8];
+    float dg[4][MC];
 #pragma unroll
     for (int g = 0; g < 4; ++g)
-      if (g < G) tmem_ld8(tlane + kColD + 16u * g, dg[g]);
+      if (g < G) tmem_ldn<MC>(tlane + kColD + 16u * g, dg[g]);
     tc_wait_ld();
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -147,18 +148,18 @@ struct RowAffine {
         const float4 x0 = lds128f(rs.pxs + 32u * g), x1 = lds128f(rs.pxs + 32u * g + 16u);
         const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-        for (int m = 0; m < 8; ++m) acc[m] = fmaf(rs.ps[g], dg[g][m], fmaf(rs.pb[g], xs[m], acc[m]));
+        for (int m = 0; m < MC; ++m) acc[m] = fmaf(rs.ps[g], dg[g][m], fmaf(rs.pb[g], xs[m], acc[m]));
       }
     }
   }
 
-  static __device__ __forceinline__ void issue_step(const RowArgs &a, uint32_t tmem, uint32_t acol, uint32_t xaddr,
-                                                    uint32_t, int) {
-    const int G = 128 / a.group_size, per = a.group_size / 16;  // MMAs per group
-    for (int g = 0; g < G; ++g)
-      for (int j = 0; j < per; ++j)
-        umma_f16(tmem + kColD + 16u * g, acol + (uint32_t)(g * per + j) * 8u,
-                 make_bdesc(xaddr + (uint32_t)(g * per + j) * 256u, 0u), kIdescF16, j > 0 ? 1u : 0u);
+  static __device__ __forceinline__ void issue_step(const RowArgs &a, uint32_t tmem, uint32_t acol, uint64_t xdesc,
+                                                    uint64_t, int) {
+    const int per = a.group_size / 16;  // MMAs per group; eight MMAs a step
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      umma_f16(tmem + kColD + 16u * (uint32_t)(j / per), acol + 8u * j, xdesc + (uint64_t)(j * 16), kIdescF16,
+               (j % per) != 0 ? 1u : 0u);
   }
 
   // ---- activation warp ---------------------------------------------------------------------------

@@ -99,20 +99,20 @@ struct RowIQ2XS {
   static __device__ __forceinline__ void store_min(const RowState &, int, uint32_t) {}
   static __device__ __forceinline__ void advance(RowState &rs, int, uint32_t) { rs.ps = rs.cs; }
 
-  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &, float (&acc)[8],
+  template <int MC>
+  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &, float (&acc)[MC],
                                                       uint32_t tlane) {
-    float d[8];
-    tmem_ld8(tlane + kColD, d);
+    float d[MC];
+    tmem_ldn<MC>(tlane + kColD, d);
     tc_wait_ld();
 #pragma unroll
-    for (int m = 0; m < 8; ++m) acc[m] = fmaf(rs.ps, d[m], acc[m]);
+    for (int m = 0; m < MC; ++m) acc[m] = fmaf(rs.ps, d[m], acc[m]);
   }
 
-  static __device__ __forceinline__ void issue_step(const RowArgs &, uint32_t tmem, uint32_t acol, uint32_t xaddr,
-                                                    uint32_t, int) {
+  static __device__ __forceinline__ void issue_step(const RowArgs &, uint32_t tmem, uint32_t acol, uint64_t xdesc,
+                                                    uint64_t, int) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      umma_f16(tmem + kColD, acol + 8u * j, make_bdesc(xaddr + 256u * j, 0u), kIdescF16, j > 0 ? 1u : 0u);
+    for (int j = 0; j < 8; ++j) umma_f16(tmem + kColD, acol + 8u * j, xdesc + (uint64_t)(j * 16), kIdescF16, j > 0 ? 1u : 0u);
   }
 
   // activation warp: same slot order as Q4_K (0, 2, 1, 3 inside every four k), no group sums

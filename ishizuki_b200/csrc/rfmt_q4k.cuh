@@ -95,35 +95,38 @@ struct RowQ4K {
     rs.prev_hh = hh;
   }
 
-  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &a, float (&acc)[8],
+  template <int MC>
+  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &a, float (&acc)[MC],
                                                       uint32_t tlane) {
     (void)a;
-    float dg[4][8], dm[8];
+    float dg[4][MC], dm[MC];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) tmem_ld8(tlane + kColD + 16u * i, dg[i]);
-    if (rs.prev_hh == 1) tmem_ld8(tlane + kColDmin, dm);
+    for (int i = 0; i < 4; ++i) tmem_ldn<MC>(tlane + kColD + 16u * i, dg[i]);
+    if (rs.prev_hh == 1) tmem_ldn<MC>(tlane + kColDmin, dm);
     tc_wait_ld();
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int m = 0; m < 8; ++m) acc[m] = fmaf(rs.ps[i], dg[i][m], acc[m]);
+      for (int m = 0; m < MC; ++m) acc[m] = fmaf(rs.ps[i], dg[i][m], acc[m]);
     if (rs.prev_hh == 1) {
 #pragma unroll
-      for (int m = 0; m < 8; ++m) acc[m] = fmaf(-rs.pmin, dm[m], acc[m]);
+      for (int m = 0; m < MC; ++m) acc[m] = fmaf(-rs.pmin, dm[m], acc[m]);
     }
   }
 
   // one thread: the nine MMAs of a step
-  static __device__ __forceinline__ void issue_step(const RowArgs &a, uint32_t tmem, uint32_t acol, uint32_t xaddr,
-                                                    uint32_t maddr, int hh) {
+  // xdesc / mdesc: descriptors of the step's first x core matrix and of its group-sum operand; a
+  // later MMA's operand is 256 bytes further, i.e. 16 more in the descriptor's address field
+  static __device__ __forceinline__ void issue_step(const RowArgs &a, uint32_t tmem, uint32_t acol, uint64_t xdesc,
+                                                    uint64_t mdesc, int hh) {
     (void)a;
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int s = 0; s < 2; ++s)
-        umma_f16(tmem + kColD + 16u * i, acol + 16u * i + 8u * s, make_bdesc(xaddr + (uint32_t)(i * 2 + s) * 256u, 0u),
-                 kIdescF16, (uint32_t)s);
-    umma_f16(tmem + kColDmin, tmem + kColAmin, make_bdesc(maddr, 0u), kIdescF16, (uint32_t)hh);
+        umma_f16(tmem + kColD + 16u * i, acol + 16u * i + 8u * s, xdesc + (uint64_t)((i * 2 + s) * 16), kIdescF16,
+                 (uint32_t)s);
+    umma_f16(tmem + kColDmin, tmem + kColAmin, mdesc, kIdescF16, (uint32_t)hh);
   }
 
   // activation warp, first half: the stage's slice of x into registers. Lane (m = lane % 8,

@@ -84,26 +84,26 @@ struct RowQ6K {
     for (int g = 0; g < 8; ++g) rs.ps[g] = rs.cs[g];
   }
 
-  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &, float (&acc)[8],
+  template <int MC>
+  static __device__ __forceinline__ void consume_step(const RowState &rs, const RowArgs &, float (&acc)[MC],
                                                       uint32_t tlane) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      float dg[4][8];
+      float dg[4][MC];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) tmem_ld8(tlane + kColD + 16u * (4 * half + g), dg[g]);
+      for (int g = 0; g < 4; ++g) tmem_ldn<MC>(tlane + kColD + 16u * (4 * half + g), dg[g]);
       tc_wait_ld();
 #pragma unroll
       for (int g = 0; g < 4; ++g)
 #pragma unroll
-        for (int m = 0; m < 8; ++m) acc[m] = fmaf(rs.ps[4 * half + g], dg[g][m], acc[m]);
+        for (int m = 0; m < MC; ++m) acc[m] = fmaf(rs.ps[4 * half + g], dg[g][m], acc[m]);
     }
   }
 
-  static __device__ __forceinline__ void issue_step(const RowArgs &, uint32_t tmem, uint32_t acol, uint32_t xaddr,
-                                                    uint32_t, int) {
+  static __device__ __forceinline__ void issue_step(const RowArgs &, uint32_t tmem, uint32_t acol, uint64_t xdesc,
+                                                    uint64_t, int) {
 #pragma unroll
-    for (int g = 0; g < 8; ++g)
-      umma_f16(tmem + kColD + 16u * g, acol + 8u * g, make_bdesc(xaddr + 256u * g, 0u), kIdescF16, 0u);
+    for (int g = 0; g < 8; ++g) umma_f16(tmem + kColD + 16u * g, acol + 8u * g, xdesc + (uint64_t)(g * 16), kIdescF16, 0u);
   }
 
   static constexpr int kXRegs = 16;
