@@ -12,6 +12,8 @@
 
 #include "../../include/ishizuki_cuda.h"
 #include "dequant.cuh"
+#include "ffmt_q4k.cuh"
+#include "ishi_fragstream.cuh"
 #include "ishi_rowstream.cuh"
 #include "rfmt_affine.cuh"
 #include "rfmt_iq2xs.cuh"
@@ -43,6 +45,13 @@ struct RowPlan {
   size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
 };
 
+// Launch plan of the warp-level kernel (fragment-order tiles, 16-row panels).
+struct FragPlan {
+  bool ok = false;
+  int units = 0, S = 1, P = 0, Gc = 1, SL = 2, W = 1, umax = 0, tile_bytes = 0, ring_stride = 0, grid = 0;
+  size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
+};
+
 }  // namespace
 
 struct ishi_ctx {
@@ -65,7 +74,8 @@ struct ishi_projection {
   ishi_ctx *ctx = nullptr;
   ishi_weight_desc d;
   int fmt = 0;
-  RowPlan plan;
+  RowPlan plan;          // tcgen05 kernel (formats without a fragment decoder)
+  FragPlan frag;         // warp-level kernel
   Workspace ws;          // this projection's own scratch and tiled weight: apply never allocates
   __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
   int64_t weight_bytes = 0;
@@ -351,6 +361,115 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
   return ISHI_OK;
 }
 
+// ---- warp-level kernel: plan, tiling, launch ------------------------------------------------------
+
+bool has_frag_kernel(int fmt) { return fmt == ISHI_GGML_Q4_K; }
+
+bool make_frag_plan(const ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
+  const int fmt = format_of(d);
+  if (!has_frag_kernel(fmt)) return false;
+  const int xbytes = FragQ4K::kXBytes;
+  pl->tile_bytes = FragQ4K::kTileBytes;
+  pl->ring_stride = (pl->tile_bytes + 127) & ~127;
+  pl->units = (int)(d.k / 256);
+  pl->P = (int)((d.n + kFragRows - 1) / kFragRows);
+  pl->tiles_bytes = (size_t)pl->P * pl->units * pl->tile_bytes;
+  const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
+  int best_s = 0, best_grid = 0;
+  for (int s = 1; s <= pl->units && s <= 16; ++s) {
+    const int umax = (pl->units + s - 1) / s;
+    const int per = (umax + kFragMaxWarps - 1) / kFragMaxWarps;
+    const int w = (umax + per - 1) / per;
+    const size_t smem = (size_t)umax * xbytes + (size_t)w * (1024 + kFragRing * pl->ring_stride);
+    if (smem > budget) continue;
+    const int grid = (ctx->sm_count / s) * s;
+    if (best_s == 0 || grid > best_grid) {
+      best_s = s;
+      best_grid = grid;
+    }
+    if (best_s != 0 && s >= best_s + 2) break;  // a little further only to use more SMs
+  }
+  if (best_s == 0) return false;
+  pl->S = best_s;
+  pl->umax = (pl->units + pl->S - 1) / pl->S;
+  const int per = (pl->umax + kFragMaxWarps - 1) / kFragMaxWarps;
+  pl->W = (pl->umax + per - 1) / per;
+  pl->smem = (size_t)pl->umax * xbytes + (size_t)pl->W * (1024 + kFragRing * pl->ring_stride);
+  pl->Gc = std::max(1, ctx->sm_count / pl->S);
+  pl->grid = pl->Gc * pl->S;
+  const int umin = pl->units / pl->S;
+  const int dense_slots = (pl->Gc + pl->P - 1) / pl->P + 1;
+  pl->SL = (long long)pl->P * umin >= pl->Gc ? dense_slots : std::max(pl->umax, dense_slots);
+  pl->scratch_floats = (size_t)pl->P * pl->S * pl->SL * 128;
+  pl->counters = (size_t)pl->P;
+  pl->ok = true;
+  return true;
+}
+
+ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weight_desc &d, uint8_t *dst, cudaStream_t st) {
+  FragSrc src;
+  memset(&src, 0, sizeof(src));
+  src.w = static_cast<const uint8_t *>(d.weight_dev);
+  src.w_row_bytes = (long long)(d.k / 256) * type_size(d.ggml_type);
+  src.N = d.n;
+  const long long total = (long long)pl.P * pl.units * (pl.tile_bytes / 2);
+  const int grid = (int)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
+  prepare_frag_kernel<FragQ4K><<<grid, 256, 0, st>>>(src, pl.units, pl.tile_bytes, dst);
+  ISHI_CUDA(ctx, cudaGetLastError());
+  return ISHI_OK;
+}
+
+template <class Fmt, int MODE>
+ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args, cudaStream_t st) {
+  auto kern = frag_kernel<Fmt, MODE>;
+  static bool configured[64] = {false};
+  static std::mutex once;
+  {
+    std::lock_guard<std::mutex> g(once);
+    if (!configured[ctx->device & 63]) {
+      ISHI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          std::min(kSmemPerSm, ctx->smem_optin) - 1024));
+      configured[ctx->device & 63] = true;
+    }
+  }
+  kern<<<pl.grid, pl.W * 32, pl.smem, st>>>(args);
+  ISHI_CUDA(ctx, cudaGetLastError());
+  return ISHI_OK;
+}
+
+// rows 1...16 through the warp-level kernel; gemv picks the CUDA-core variant for a single row
+ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, const ishi_weight_desc &d, const void *x,
+                     int rows, void *y, long long ldy, int flags, bool gemv, cudaStream_t st) {
+  for (int r0 = 0; r0 < rows; r0 += 8) {
+    FragArgs a;
+    memset(&a, 0, sizeof(a));
+    a.tiles = ws.tiles;
+    a.tile_bytes = pl.tile_bytes;
+    a.ring_stride = pl.ring_stride;
+    a.x = static_cast<const __half *>(x) + (long long)r0 * d.k;
+    a.y = static_cast<__half *>(y) + ((flags & ISHI_OUT_TRANSPOSED) ? (long long)r0 : (long long)r0 * ldy);
+    a.ldy = ldy;
+    a.out_transposed = (flags & ISHI_OUT_TRANSPOSED) ? 1 : 0;
+    a.scratch = ws.scratch;
+    a.counters = ws.counters;
+    a.M = std::min(8, rows - r0);
+    a.N = (int)d.n;
+    a.K = (int)d.k;
+    a.units = pl.units;
+    a.S = pl.S;
+    a.P = pl.P;
+    a.Gc = pl.Gc;
+    a.SL = pl.SL;
+    a.W = pl.W;
+    a.umax = pl.umax;
+    a.group_size = d.group_size;
+    a.scale_dtype = d.scale_dtype;
+    ishi_status s = (gemv && rows == 1) ? launch_frag<FragQ4K, 1>(ctx, pl, a, st) : launch_frag<FragQ4K, 0>(ctx, pl, a, st);
+    if (s != ISHI_OK) return s;
+  }
+  return ISHI_OK;
+}
+
 ishi_status check_io(ishi_ctx *ctx, const void *x, int rows, const void *y, int max_rows) {
   if (!x || !y) return fail(ctx, ISHI_E_INVALID, "null pointer");
   if (!aligned16(x)) return fail(ctx, ISHI_E_INVALID, "x must be 16-byte aligned");
@@ -359,12 +478,21 @@ ishi_status check_io(ishi_ctx *ctx, const void *x, int rows, const void *y, int 
 }
 
 // Kernel-level product on a caller's raw weight: re-tiles it into the context's buffer, then runs.
-ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x, int rows, void *y, cudaStream_t st) {
+ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x, int rows, void *y, bool gemv,
+                        cudaStream_t st) {
   int64_t wb = 0;
   ishi_status s = check_desc(ctx, d, &wb);
   if (s != ISHI_OK) return s;
   std::lock_guard<std::mutex> g(ctx->lock);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  FragPlan fp;
+  if (make_frag_plan(ctx, d, &fp)) {
+    s = ensure_workspace(ctx, &ctx->ws, fp.scratch_floats, fp.counters, fp.tiles_bytes);
+    if (s != ISHI_OK) return s;
+    s = tile_weight_frag(ctx, fp, d, ctx->ws.tiles, st);
+    if (s != ISHI_OK) return s;
+    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, st);
+  }
   RowPlan pl;
   if (!make_row_plan(ctx, d, &pl)) return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
   s = ensure_workspace(ctx, &ctx->ws, pl.scratch_floats, pl.counters, pl.tiles_bytes);
@@ -375,7 +503,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
 }
 
 ishi_status ggml_raw(ishi_ctx *ctx, const void *x, int rows, const void *blocks, int64_t blocks_bytes, int type,
-                     int64_t n, int64_t k, void *y, void *stream) {
+                     int64_t n, int64_t k, void *y, bool gemv, void *stream) {
   if (!ctx) return ISHI_E_INVALID;
   ishi_status s = check_io(ctx, x, rows, y, 16);
   if (s != ISHI_OK) return s;
@@ -387,7 +515,7 @@ ishi_status ggml_raw(ishi_ctx *ctx, const void *x, int rows, const void *blocks,
   d.k = k;
   d.weight_dev = blocks;
   d.weight_bytes = blocks_bytes;
-  return raw_product(ctx, d, x, rows, y, static_cast<cudaStream_t>(stream));
+  return raw_product(ctx, d, x, rows, y, gemv, static_cast<cudaStream_t>(stream));
 }
 
 ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void *y, int64_t ldy, int flags,
@@ -398,6 +526,7 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   const int64_t need_ld = (flags & ISHI_OUT_TRANSPOSED) ? rows : p->d.n;
   if (ldy < need_ld) return fail(ctx, ISHI_E_SHAPE, "ldy %lld shorter than %lld", (long long)ldy, (long long)need_ld);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (p->frag.ok) return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, ctx->route == ISHI_ROUTE_GEMV, st);
   return run_rows(ctx, p->plan, p->ws, p->fmt, p->d, x, rows, y, ldy, flags, st);
 }
 
@@ -566,12 +695,14 @@ ishi_status ishi_hadamard_rotate(ishi_ctx *ctx, const void *x, int64_t rows, int
 
 ishi_status ishi_ggml_matmul_few(ishi_ctx *ctx, const void *x, int rows, const void *blocks, int64_t blocks_bytes,
                                  int type, int64_t n, int64_t k, void *y, void *stream) {
-  return ggml_raw(ctx, x, rows, blocks, blocks_bytes, type, n, k, y, stream);
+  return ggml_raw(ctx, x, rows, blocks, blocks_bytes, type, n, k, y, false, stream);
 }
 
 ishi_status ishi_ggml_matvec(ishi_ctx *ctx, const void *x, int rows, const void *blocks, int64_t blocks_bytes,
                              int type, int64_t n, int64_t k, void *y, void *stream) {
-  return ggml_raw(ctx, x, rows, blocks, blocks_bytes, type, n, k, y, stream);
+  // a single row runs on CUDA cores where the format has that kernel; more rows, or other
+  // formats, take the tensor-core kernel
+  return ggml_raw(ctx, x, rows, blocks, blocks_bytes, type, n, k, y, true, stream);
 }
 
 ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x, int rows, const void *w, const void *scales,
@@ -593,7 +724,7 @@ ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x, int rows, const voi
   d.weight_bytes = (bits >= 2 && bits <= 8 && n > 0 && k > 0) ? n * k * bits / 8 : 0;
   d.scales_dev = scales;
   d.biases_dev = biases;
-  return raw_product(ctx, d, x, rows, y, static_cast<cudaStream_t>(stream));
+  return raw_product(ctx, d, x, rows, y, route == ISHI_ROUTE_GEMV, static_cast<cudaStream_t>(stream));
 }
 
 // ---- projection: the PackedLinear counterpart ---------------------------------------------------
@@ -613,13 +744,19 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
   p->d = *desc;
   p->fmt = format_of(*desc);
   p->weight_bytes = wb;
-  if (!make_row_plan(ctx, p->d, &p->plan)) {
-    delete p;
-    return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)desc->k);
+  // Re-tile the weight once, for the kernel this format runs on; the caller's buffer is not read
+  // again afterwards.
+  if (make_frag_plan(ctx, p->d, &p->frag)) {
+    s = ensure_workspace(ctx, &p->ws, p->frag.scratch_floats, p->frag.counters, p->frag.tiles_bytes);
+    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, p->d, p->ws.tiles, 0);
+  } else {
+    if (!make_row_plan(ctx, p->d, &p->plan)) {
+      delete p;
+      return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)desc->k);
+    }
+    s = ensure_workspace(ctx, &p->ws, p->plan.scratch_floats, p->plan.counters, p->plan.tiles_bytes);
+    if (s == ISHI_OK) s = tile_weight(ctx, p->plan, p->d.n, p->ws.tiles, 0);
   }
-  s = ensure_workspace(ctx, &p->ws, p->plan.scratch_floats, p->plan.counters, p->plan.tiles_bytes);
-  // Re-tile the weight once; the caller's buffer is not read again afterwards.
-  if (s == ISHI_OK) s = tile_weight(ctx, p->plan, p->d.n, p->ws.tiles, 0);
   if (s == ISHI_OK) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "tiling the weight: %s", cudaGetErrorString(e));
