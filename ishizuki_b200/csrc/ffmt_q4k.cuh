@@ -133,18 +133,21 @@ struct FragQ4K {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint4 w = lds128(tile + (uint32_t)j * 512u + (uint32_t)lane * 16u);  // row g: w.x, w.y; row g + 8: w.z, w.w
+      const uint32_t xj = xl ^ (uint32_t)(j << 5);  // the chunk's staging swizzle; k-steps follow at 256-byte steps
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const uint32_t mask = h ? 0x00f000f0u : 0x000f000fu;
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
+        float part[4];
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           const uint32_t x0 = s ? w.y : w.x, x1 = s ? w.w : w.z;
           const uint32_t a0 = x0 & mask, a1 = x1 & mask, a2 = (x0 >> 8) & mask, a3 = (x1 >> 8) & mask;
-          const uint2 b = lds64((xl + (uint32_t)(4 * j + 2 * h + s) * 256u) ^ (uint32_t)(j << 5));
+          const uint2 b = lds64(xj + (uint32_t)(4 * j + 2 * h + s) * 256u);
           if (MODE == 0) {
-            mma16816(part, a0, a1, a2, a3, b.x, b.y);
+            if (s == 0) mma16816_first(part, a0, a1, a2, a3, b.x, b.y);
+            else mma16816(part, a0, a1, a2, a3, b.x, b.y);
           } else {
+            if (s == 0) part[0] = part[1] = part[2] = part[3] = 0.f;
             part[0] = fmaf(half_lo(a0), half_lo(b.x), part[0]);
             part[0] = fmaf(half_hi(a0), half_hi(b.x), part[0]);
             part[0] = fmaf(half_lo(a2), half_lo(b.y), part[0]);
@@ -172,8 +175,8 @@ struct FragQ4K {
       const uint32_t msel = (t & 1) ? 0x4342u : 0x4140u;  // (byte 2t', zero, byte 2t'+1, zero), t' = t % 2
       const uint32_t ma = prmt(m0w, 0u, msel), mb = prmt(m1w, 0u, msel);  // (m[2t], m[2t+1]) as fp16 m * 2^-24
       const uint2 xs = lds64(xu + 4096u + (uint32_t)lane * 8u);
-      float cm[4] = {0.f, 0.f, 0.f, 0.f};
-      mma16816(cm, ma, mb, ma, mb, xs.x, xs.y);
+      float cm[4];
+      mma16816_first(cm, ma, mb, ma, mb, xs.x, xs.y);
       const float n0 = half_bits_to_float(h0.x >> 16) * 16777216.f, n1 = half_bits_to_float(h1.x >> 16) * 16777216.f;
       acc[0] += d0 * accu[0] - n0 * cm[0];
       acc[1] += d0 * accu[1] - n0 * cm[1];

@@ -7,7 +7,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <tuple>
 #include <new>
 
 #include "../../include/ishizuki_cuda.h"
@@ -45,11 +47,12 @@ struct RowPlan {
   size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
 };
 
-// Launch plan of the warp-level kernel (fragment-order tiles, 16-row panels).
+// Launch plan of the warp-level kernel (fragment-order tiles, 16-row panels, clusters of S CTAs).
 struct FragPlan {
   bool ok = false;
-  int units = 0, S = 1, P = 0, Gc = 1, SL = 2, W = 1, umax = 0, tile_bytes = 0, ring_stride = 0, grid = 0;
-  size_t smem = 0, scratch_floats = 0, counters = 0, tiles_bytes = 0;
+  int units = 0, S = 1, P = 0, NC = 1, Wu = 1, PP = 1, SPW = 1, umax = 0, tile_bytes = 0;
+  size_t smem = 0, tiles_bytes = 0;
+  double cost = 0;
 };
 
 }  // namespace
@@ -365,44 +368,106 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
 
 bool has_frag_kernel(int fmt) { return fmt == ISHI_GGML_Q4_K; }
 
-bool make_frag_plan(const ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
+template <class Fmt, int MODE>
+ishi_status configure_frag(ishi_ctx *ctx) {
+  static bool configured[64] = {false};
+  static std::mutex once;
+  std::lock_guard<std::mutex> g(once);
+  if (!configured[ctx->device & 63]) {
+    ISHI_CUDA(ctx, cudaFuncSetAttribute(frag_kernel<Fmt, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        std::min(kSmemPerSm, ctx->smem_optin) - 1024));
+    configured[ctx->device & 63] = true;
+  }
+  return ISHI_OK;
+}
+
+// how many clusters of s CTAs with this much shared memory the device runs at once
+int max_frag_clusters(ishi_ctx *ctx, int s, int warps, size_t smem) {
+  if (s == 1) return ctx->sm_count;
+  static std::map<std::tuple<int, int, int, size_t>, int> cache;
+  static std::mutex lock;
+  std::lock_guard<std::mutex> g(lock);
+  const auto key = std::make_tuple(ctx->device, s, warps, smem);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(s * ctx->sm_count), 1, 1);
+  cfg.blockDim = dim3((unsigned)(warps * 32), 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute at;
+  at.id = cudaLaunchAttributeClusterDimension;
+  at.val.clusterDim.x = (unsigned)s;
+  at.val.clusterDim.y = 1;
+  at.val.clusterDim.z = 1;
+  cfg.attrs = &at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, frag_kernel<FragQ4K, 0>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cache[key] = n;
+  return n;
+}
+
+// Picks the K split S (= cluster size), the warps per panel, the panels a CTA works on in
+// parallel and the panels per group. The estimate counts tile times on the longest warp (panels of
+// the fullest cluster x units per warp), stretched where the warps outnumber what the issue slots
+// sustain.
+bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   const int fmt = format_of(d);
   if (!has_frag_kernel(fmt)) return false;
+  if (configure_frag<FragQ4K, 0>(ctx) != ISHI_OK || configure_frag<FragQ4K, 1>(ctx) != ISHI_OK) return false;
   const int xbytes = FragQ4K::kXBytes;
-  pl->tile_bytes = FragQ4K::kTileBytes;
-  pl->ring_stride = (pl->tile_bytes + 127) & ~127;
-  pl->units = (int)(d.k / 256);
-  pl->P = (int)((d.n + kFragRows - 1) / kFragRows);
-  pl->tiles_bytes = (size_t)pl->P * pl->units * pl->tile_bytes;
+  FragPlan best;
+  const int tile_bytes = FragQ4K::kTileBytes;
+  const int units = (int)(d.k / 256);
+  const int P = (int)((d.n + kFragRows - 1) / kFragRows);
   const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
-  int best_s = 0, best_grid = 0;
-  for (int s = 1; s <= pl->units && s <= 16; ++s) {
-    const int umax = (pl->units + s - 1) / s;
-    const int per = (umax + kFragMaxWarps - 1) / kFragMaxWarps;
-    const int w = (umax + per - 1) / per;
-    const size_t smem = (size_t)umax * xbytes + (size_t)w * (1024 + kFragRing * pl->ring_stride);
-    if (smem > budget) continue;
-    const int grid = (ctx->sm_count / s) * s;
-    if (best_s == 0 || grid > best_grid) {
-      best_s = s;
-      best_grid = grid;
+  const char *force = getenv("ISHI_FRAG_PLAN");  // "S,per,PP" for tuning runs
+  int fs = 0, fper = 0, fpp = 0;
+  if (force) sscanf(force, "%d,%d,%d", &fs, &fper, &fpp);
+  for (int s = 1; s <= kFragMaxSplit && s <= units; ++s) {
+    if (fs && s != fs) continue;
+    const int umax = (units + s - 1) / s;
+    const int per_min = (umax + kFragMaxWarps - 1) / kFragMaxWarps;
+    for (int per = per_min; per <= std::min(per_min + 2, kFragGroup); ++per) {
+      if (fper && per != fper) continue;
+      const int wu = (umax + per - 1) / per;
+      for (int pp = 1; pp <= 4 && wu * pp <= kFragMaxWarps; pp *= 2) {
+        if (fpp && pp != fpp) continue;
+        FragPlan c;
+        c.units = units;
+        c.P = P;
+        c.S = s;
+        c.tile_bytes = tile_bytes;
+        c.umax = umax;
+        c.Wu = wu;
+        c.PP = pp;
+        const int w = wu * pp;
+        for (c.SPW = std::max(1, kFragGroup / per); c.SPW >= 1; --c.SPW) {
+          c.smem = frag_smem_bytes(umax, xbytes, w, pp, c.SPW, s, tile_bytes);
+          if (c.smem <= budget) break;
+        }
+        if (c.SPW < 1) continue;
+        // one CTA per SM: two would stage the activations twice and split the issue slots
+        c.NC = std::min(std::min(max_frag_clusters(ctx, s, w, c.smem), ctx->sm_count / s), P);
+        if (c.NC < 1) continue;
+        const int panels = (P + c.NC - 1) / c.NC;
+        const double tile_time = std::max(1.0, w / 12.0) * (1.0 + 2.0 / w);  // issue-bound past ~12 warps; few warps hide less latency
+        c.cost = (double)((panels + pp - 1) / pp) * per * tile_time + 0.05 * umax + 0.5 / c.SPW;
+        c.ok = true;
+        if (!best.ok || c.cost < best.cost) best = c;
+      }
     }
-    if (best_s != 0 && s >= best_s + 2) break;  // a little further only to use more SMs
   }
-  if (best_s == 0) return false;
-  pl->S = best_s;
-  pl->umax = (pl->units + pl->S - 1) / pl->S;
-  const int per = (pl->umax + kFragMaxWarps - 1) / kFragMaxWarps;
-  pl->W = (pl->umax + per - 1) / per;
-  pl->smem = (size_t)pl->umax * xbytes + (size_t)pl->W * (1024 + kFragRing * pl->ring_stride);
-  pl->Gc = std::max(1, ctx->sm_count / pl->S);
-  pl->grid = pl->Gc * pl->S;
-  const int umin = pl->units / pl->S;
-  const int dense_slots = (pl->Gc + pl->P - 1) / pl->P + 1;
-  pl->SL = (long long)pl->P * umin >= pl->Gc ? dense_slots : std::max(pl->umax, dense_slots);
-  pl->scratch_floats = (size_t)pl->P * pl->S * pl->SL * 128;
-  pl->counters = (size_t)pl->P;
-  pl->ok = true;
+  if (!best.ok) return false;
+  best.tiles_bytes = (size_t)P * units * tile_bytes;
+  if (getenv("ISHI_DEBUG_PLAN"))
+    fprintf(stderr, "ishi plan n=%lld k=%lld: split %d, clusters %d, warps %d x %d, panels per warp and group %d, smem %zu\n",
+            (long long)d.n, (long long)d.k, best.S, best.NC, best.Wu, best.PP, best.SPW, best.smem);
+  *pl = best;
   return true;
 }
 
@@ -421,19 +486,20 @@ ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weigh
 
 template <class Fmt, int MODE>
 ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args, cudaStream_t st) {
-  auto kern = frag_kernel<Fmt, MODE>;
-  static bool configured[64] = {false};
-  static std::mutex once;
-  {
-    std::lock_guard<std::mutex> g(once);
-    if (!configured[ctx->device & 63]) {
-      ISHI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          std::min(kSmemPerSm, ctx->smem_optin) - 1024));
-      configured[ctx->device & 63] = true;
-    }
-  }
-  kern<<<pl.grid, pl.W * 32, pl.smem, st>>>(args);
-  ISHI_CUDA(ctx, cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(pl.NC * pl.S), 1, 1);
+  cfg.blockDim = dim3((unsigned)(pl.Wu * pl.PP * 32), 1, 1);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at;
+  at.id = cudaLaunchAttributeClusterDimension;
+  at.val.clusterDim.x = (unsigned)pl.S;
+  at.val.clusterDim.y = 1;
+  at.val.clusterDim.z = 1;
+  cfg.attrs = &at;
+  cfg.numAttrs = 1;
+  ISHI_CUDA(ctx, cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, MODE>, args));
   return ISHI_OK;
 }
 
@@ -444,26 +510,26 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     FragArgs a;
     memset(&a, 0, sizeof(a));
     a.tiles = ws.tiles;
-    a.tile_bytes = pl.tile_bytes;
-    a.ring_stride = pl.ring_stride;
     a.x = static_cast<const __half *>(x) + (long long)r0 * d.k;
     a.y = static_cast<__half *>(y) + ((flags & ISHI_OUT_TRANSPOSED) ? (long long)r0 : (long long)r0 * ldy);
     a.ldy = ldy;
     a.out_transposed = (flags & ISHI_OUT_TRANSPOSED) ? 1 : 0;
-    a.scratch = ws.scratch;
-    a.counters = ws.counters;
     a.M = std::min(8, rows - r0);
     a.N = (int)d.n;
     a.K = (int)d.k;
     a.units = pl.units;
     a.S = pl.S;
     a.P = pl.P;
-    a.Gc = pl.Gc;
-    a.SL = pl.SL;
-    a.W = pl.W;
+    a.NC = pl.NC;
+    a.Wu = pl.Wu;
+    a.PP = pl.PP;
+    a.SPW = pl.SPW;
+    a.pp_shift = pl.PP == 4 ? 2 : pl.PP == 2 ? 1 : 0;
+    a.inv_s = (65536 + pl.S - 1) / pl.S;
     a.umax = pl.umax;
     a.group_size = d.group_size;
     a.scale_dtype = d.scale_dtype;
+    a.err = ctx->err_dev;
     ishi_status s = (gemv && rows == 1) ? launch_frag<FragQ4K, 1>(ctx, pl, a, st) : launch_frag<FragQ4K, 0>(ctx, pl, a, st);
     if (s != ISHI_OK) return s;
   }
@@ -487,7 +553,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   FragPlan fp;
   if (make_frag_plan(ctx, d, &fp)) {
-    s = ensure_workspace(ctx, &ctx->ws, fp.scratch_floats, fp.counters, fp.tiles_bytes);
+    s = ensure_workspace(ctx, &ctx->ws, 0, 0, fp.tiles_bytes);
     if (s != ISHI_OK) return s;
     s = tile_weight_frag(ctx, fp, d, ctx->ws.tiles, st);
     if (s != ISHI_OK) return s;
@@ -747,7 +813,7 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
   // Re-tile the weight once, for the kernel this format runs on; the caller's buffer is not read
   // again afterwards.
   if (make_frag_plan(ctx, p->d, &p->frag)) {
-    s = ensure_workspace(ctx, &p->ws, p->frag.scratch_floats, p->frag.counters, p->frag.tiles_bytes);
+    s = ensure_workspace(ctx, &p->ws, 0, 0, p->frag.tiles_bytes);
     if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, p->d, p->ws.tiles, 0);
   } else {
     if (!make_row_plan(ctx, p->d, &p->plan)) {

@@ -15,38 +15,42 @@
 // in every k-step, the four k positions the format's decoder assigns to t. Same bytes as the raw
 // weight, different order.
 //
-// Work. K is cut into S column ranges, the grid into S groups of Gc persistent CTAs; (panel,
-// unit) pairs of a column range are dealt to its CTAs in equal contiguous runs. Inside a CTA the
-// activations of the column range are staged once into shared memory in fragment order, and warp
-// w takes the units u = w, w + W, ... of every panel. Each warp streams its tiles through a
-// private ring in shared memory with cp.async (16 bytes per lane), so there is no producer warp
-// and no cross-warp wait on the data path; the warps meet once per panel (a CTA barrier) to add
-// their partial tiles. A panel whose units are spread over several CTAs goes through fp32
-// scratch slots and an arrival counter; the last contributor adds the slots in slot order. That
-// commit is deferred to the end of the CTA so its latency is paid once, not per panel.
+// Work. K is cut into S column ranges and the kernel is launched as thread-block clusters of S
+// CTAs: CTA r of a cluster stages the activations of column range r into shared memory once, in
+// fragment order, and all CTAs of a cluster walk the same run of 16-row panels, dealt to the
+// clusters in equal contiguous runs. Inside a CTA warp w takes the units u = w, w + W, ... of every
+// panel and streams its tiles through a private ring in shared memory with cp.async (16 bytes per
+// lane): no producer warp, no cross-warp wait on the data path. The warps meet once per group of
+// panels (a CTA barrier) to add their partial tiles; the CTA's partial panel then goes into the
+// shared memory of the panel's leader CTA (distributed shared memory), and after a cluster
+// barrier, whose wait is deferred by one group so that it overlaps the next group's tiles, the
+// leader adds the S partials in rank order and writes y. No global scratch, no atomics, every y
+// element written once, the summation order fixed.
 #pragma once
 #include "ishi_stream.cuh"
 
 namespace ishi {
 
 constexpr int kFragRows = 16;
-constexpr int kFragMaxWarps = 16;
-constexpr int kFragRing = 4;  // tiles per warp-private ring: three in flight while one is decoded
+constexpr int kFragMaxWarps = 20;
+constexpr int kFragRing = 3;      // tiles per warp-private ring: two in flight while one is decoded
+constexpr int kFragGroup = 4;     // most panels of one warp between two CTA barriers
+constexpr int kFragMaxSplit = 8;  // portable cluster size
 
 struct FragArgs {
-  const uint8_t *tiles;  // [P][units][tile_bytes]
-  int tile_bytes;        // 16 rows x bytes of one unit
-  int ring_stride;       // tile_bytes rounded up to 128
+  const uint8_t *tiles;  // [P][units][tile bytes]
   const __half *x;
   __half *y;
   long long ldy;
   int out_transposed;
-  float *scratch;          // [P][S][SL][128]
-  unsigned int *counters;  // [P]
   int M, N, K;
-  int units, S, P, Gc, SL, W;
-  int umax;                // most units in a column range
+  int units, S, P, NC;  // NC clusters of S CTAs
+  int Wu, PP, SPW;      // warps per panel, panels in parallel (1, 2 or 4; Wu * PP warps per CTA), panels per warp and group
+  int pp_shift;         // log2(PP)
+  int inv_s;            // ceil(65536 / S): n / S = (n * inv_s) >> 16 for n < 8192
+  int umax;             // most units in a column range
   int group_size, scale_dtype;
+  int *err;             // raised when a bounded wait gives up
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
@@ -60,189 +64,261 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+// the address of this CTA's shared-memory location addr in CTA rank of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// 16 bytes into another CTA's shared memory; the bytes count as completed on that CTA's mbarrier
+// when they have landed, so the reader needs no fence: it waits for the barrier's phase
+__device__ __forceinline__ void st_async128(uint32_t addr, float4 v, uint32_t mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1,%2,%3,%4}, [%5];" ::"r"(addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(mbar)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// the execution barrier alone: no fence, so nothing waits for the copies and stores in flight
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_relaxed() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 
-__host__ __device__ inline int frag_column_begin(int c, int units, int S) { return (int)(((long long)c * units) / S); }
+__host__ __device__ inline int frag_column_begin(int c, int units, int S) { return (c * units) / S; }
+__host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_bytes + 127) & ~127; }
 
-// contributors to panel p: per column range as panel_touch(); slot order is column-major
-__host__ __device__ inline int frag_touch(int p, int c, int units, int S, int P, int Gc, long long *first) {
-  const int uc = frag_column_begin(c + 1, units, S) - frag_column_begin(c, units, S);
-  return panel_touch(p, uc, P, Gc, first);
+// shared memory of one CTA, in order: activations, partial tiles of the warps, partial panels of
+// the cluster's CTAs, two mbarriers and an abort word, the warps' rings
+__host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int SPW, int S, int tile_bytes) {
+  return (size_t)umax * xbytes + (size_t)W * SPW * 512 + 2 * (size_t)SPW * PP * S * 512 + 128 +
+         (size_t)W * kFragRing * frag_ring_stride(tile_bytes);
+}
+
+// the four accumulator registers of lane ln (g = ln / 4, t = ln % 4) of panel p: register e is
+// weight row g + 8 * (e / 2), activation row 2t + e % 2
+__device__ __forceinline__ void frag_write(const FragArgs &a, int p, int ln, float4 v) {
+  const float r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const long long n = (long long)p * kFragRows + (ln >> 2) + ((e & 2) ? 8 : 0);
+    const int m = 2 * (ln & 3) + (e & 1);
+    if (n < a.N && m < a.M) {
+      const __half h = __float2half_rn(r[e]);
+      if (a.out_transposed) a.y[n * a.ldy + m] = h;
+      else a.y[(long long)m * a.ldy + n] = h;
+    }
+  }
 }
 
 // MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row.
 template <class Fmt, int MODE>
 __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kTile = Fmt::kTileBytes;
+  constexpr uint32_t kStride = (uint32_t)((kTile + 127) & ~127);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int W = a.W;
+  const int S = a.S, Wu = a.Wu, PP = a.PP, SPW = a.SPW, pp_shift = a.pp_shift;
+  const int W = Wu * PP, SP = SPW * PP;
+  const int wu = warp % Wu, wp = warp / Wu;  // this warp's unit lane and panel lane
 
-  // shared memory: activations in fragment order, partial tiles, one ring per warp
-  const uint32_t xfrag = smem_u32(smem);                                   // [umax][Fmt::kXBytes]
-  const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;            // [2][W][32 lanes][16 B]
-  const uint32_t ring = red + 2u * (uint32_t)W * 512u + (uint32_t)warp * kFragRing * (uint32_t)a.ring_stride;
+  const uint32_t xfrag = smem_u32(smem);                          // [umax][Fmt::kXBytes]
+  const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;   // [W][SPW][128 floats]
+  const uint32_t inbox = red + (uint32_t)(W * SPW) * 512u;        // [2][SP][S][128 floats]
+  const uint32_t full = inbox + 2u * (uint32_t)(SP * S) * 512u;   // two mbarriers (one per inbox half), the abort word
+  const uint32_t ring = full + 128u + (uint32_t)warp * kFragRing * kStride;
+  uint64_t *full_p = reinterpret_cast<uint64_t *>(smem + (full - xfrag));
+  volatile int *abort_word = reinterpret_cast<volatile int *>(full_p + 2);
+  const uint32_t ring_end = ring + kFragRing * kStride;
 
-  const int c = blockIdx.x / a.Gc;
-  const int j = blockIdx.x % a.Gc;
-  const int ub0 = frag_column_begin(c, a.units, a.S);
-  const int uc = frag_column_begin(c + 1, a.units, a.S) - ub0;
-  const long long Q = (long long)a.P * uc;
-  const long long q0 = (long long)j * Q / a.Gc;
-  const long long q1 = (long long)(j + 1) * Q / a.Gc;
-  const bool has_work = q1 > q0;
-  const int pa = has_work ? (int)(q0 / uc) : 0;
-  const int pb = has_work ? (int)((q1 - 1) / uc) : -1;  // inclusive
-  const int npanels = pb - pa + 1;
-  const int ua_first = (int)(q0 - (long long)pa * uc);
-  const int ub_last = (int)(q1 - (long long)pb * uc);
-  const int per = (uc - 1 - warp + W) / W;  // units of a full panel this warp owns (u = warp + i * W < uc)
-  const int perw = per > 0 ? per : 1;
+  const int r = blockIdx.x % S;  // rank in the cluster = column range
+  const int cid = blockIdx.x / S;
+  const int ub0 = frag_column_begin(r, a.units, S);
+  const int uc = frag_column_begin(r + 1, a.units, S) - ub0;
+  const int pa = (int)(((long long)cid * a.P) / a.NC);
+  const int np = (int)(((long long)(cid + 1) * a.P) / a.NC) - pa;  // the cluster's panels: pa .. pa + np - 1
+  const int per = (uc - 1 - wu + Wu) / Wu;                         // units of a panel this warp owns: wu + i * Wu < uc
+  const int npw = np > wp ? (np - wp + PP - 1) / PP : 0;           // panels this warp takes: wp, wp + PP, ...
 
-  // This warp's tile sequence: panel pa + pi, unit warp + qi * W for qi < perw, panel after panel;
-  // a tile is present when its unit lies inside the CTA's part of that panel. Every warp walks the
-  // same panels. Two cursors run over the sequence: the fetch cursor kFragRing - 1 tiles ahead of
-  // the compute cursor. No division on this path.
-  auto present = [&](int pi, int qi) -> bool {
-    const int u = warp + qi * W;
-    return pi < npanels && u < uc && (pi != 0 || u >= ua_first) && (pi != npanels - 1 || u < ub_last);
-  };
-  int f_pi = 0, f_qi = 0;
+  // Shared memory of another CTA may be written only once that CTA runs and has set up its
+  // barriers: every CTA arrives here, and waits before the first group.
+  if (S > 1) {
+    if (threadIdx.x == 0) {
+      mbar_init(full_p, 1);
+      mbar_init(full_p + 1, 1);
+      *abort_word = 0;
+      mbar_fence_init();
+    }
+    cluster_arrive();
+  }
+
+  // This warp's tile sequence: its panels in order, in each its units wu + qi * Wu. The fetch
+  // cursor runs kFragRing - 1 tiles ahead of the compute cursor.
+  int f_left = npw * per, f_qi = 0;
   uint32_t f_slot = ring;
-  const uint32_t ring_end = ring + kFragRing * (uint32_t)a.ring_stride;
-  const uint8_t *f_src = a.tiles + ((long long)pa * a.units + ub0 + warp) * (long long)a.tile_bytes;
-  const long long step_unit = (long long)W * a.tile_bytes;
-  const long long step_panel = (long long)(a.units - perw * W) * a.tile_bytes;
+  const uint8_t *f_src = a.tiles + ((long long)(pa + wp) * a.units + ub0 + wu) * (long long)kTile;
+  const long long step_unit = (long long)Wu * kTile;
+  const long long step_panel = ((long long)PP * a.units - (long long)per * Wu) * kTile;
   auto fetch = [&]() {
-    if (present(f_pi, f_qi)) {
-      for (int o = lane * 16; o < a.tile_bytes; o += 512) cp_async16(f_slot + o, f_src + o);
+    if (f_left > 0) {
+#pragma unroll
+      for (int o = 0; o + 512 <= kTile; o += 512) cp_async16(f_slot + o + lane * 16, f_src + o + lane * 16);
+      if ((kTile & 511) != 0 && lane * 16 < (kTile & 511))
+        cp_async16(f_slot + (kTile & ~511) + lane * 16, f_src + (kTile & ~511) + lane * 16);
     }
     cp_async_commit();  // one group per slot, present or not, so the wait below counts slots
+    --f_left;
     f_src += step_unit;
-    if (++f_qi == perw) {
+    if (++f_qi == per) {
       f_qi = 0;
-      ++f_pi;
       f_src += step_panel;
     }
-    f_slot += (uint32_t)a.ring_stride;
+    f_slot += kStride;
     if (f_slot == ring_end) f_slot = ring;
   };
-
-  if (has_work) {
 #pragma unroll
-    for (int i = 0; i < kFragRing - 1; ++i) fetch();
-  }
+  for (int i = 0; i < kFragRing - 1; ++i) fetch();
 
   // activations of the column range into fragment order (all warps), while the first tiles fly
   Fmt::stage_x(a, xfrag, ub0, uc);
   __syncthreads();
   // shared-memory loads are plain asm the compiler may move; tie their addresses to the waits
-  const uint32_t xf = stage_acquire(xfrag) + (uint32_t)warp * Fmt::kXBytes;
+  const uint32_t xf = stage_acquire(xfrag) + (uint32_t)wu * Fmt::kXBytes;
 
-  if (has_work) {
-    uint32_t c_slot = ring;
-    for (int pi = 0; pi < npanels; ++pi) {
-      const int p = pa + pi;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t xq = xf;
-      for (int qi = 0; qi < perw; ++qi) {
-        fetch();
-        cp_async_wait<kFragRing - 1>();  // this slot has landed (the younger groups may still be in flight)
-        __syncwarp();
-        if (present(pi, qi)) {
-          Fmt::template unit<MODE>(acc, a, stage_acquire(c_slot), xq, g, t, lane);
-          values_ready(acc[0], acc[1], acc[2], acc[3]);
-        }
-        __syncwarp();  // every lane is done reading the slot before it is refilled
-        xq += (uint32_t)W * Fmt::kXBytes;
-        c_slot += (uint32_t)a.ring_stride;
-        if (c_slot == ring_end) c_slot = ring;
+  if (S > 1) cluster_wait();
+
+  // the leader of a group's panel pn: rank pn % S
+  auto leader_of = [&](int pn) -> int { return pn - ((pn * a.inv_s) >> 16) * S; };
+  // the leaders' part of group gi: wait for the S partial panels, add them in rank order, write y
+  auto finish_group = [&](int gi) {
+    const uint32_t bar = full + (uint32_t)(gi & 1) * 8u, parity = (uint32_t)(gi >> 1) & 1u;
+    if (!mbar_try_wait_cluster(bar, parity)) {
+      bool ok = false;
+      for (uint32_t i = 0; i < kWaitSpins && !ok; ++i) {
+        ok = mbar_try_wait_cluster(bar, parity);
+        if (!ok && *abort_word != 0) break;
       }
-      if (MODE == 1) {
-        // single activation row: each lane holds partial dot products of rows g (acc[0]) and
-        // g + 8 (acc[2]) over its own k positions; add across the four lanes of a row
-        acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
-        acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
-        acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 1);
-        acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 2);
-        if (t != 0) acc[0] = acc[2] = 0.f;  // one copy per row enters the sum below (column m = 0)
-        acc[1] = acc[3] = 0.f;
+      if (!ok) {  // give up: y of this group stays wrong, the error word tells the host
+        *abort_word = 1;
+        *a.err = 1;
+        return;
       }
-      // add the warps' partial tiles: one warp per panel
-      const uint32_t rb = red + (uint32_t)(pi & 1) * (uint32_t)W * 512u;
-      sts128(rb + ((uint32_t)warp * 32u + lane) * 16u, make_float4(acc[0], acc[1], acc[2], acc[3]));
-      __syncthreads();
-      if (warp == pi % W) {
-        const uint32_t rbs = stage_acquire(rb);
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int w2 = 0; w2 < W; ++w2) {
-          const float4 v = lds128f(rbs + ((uint32_t)w2 * 32u + lane) * 16u);
-          sum[0] += v.x;
-          sum[1] += v.y;
-          sum[2] += v.z;
-          sum[3] += v.w;
-        }
-        const int ua = (p == pa) ? ua_first : 0, ub = (p == pb) ? ub_last : uc;
-        const bool whole = a.S == 1 && ua == 0 && ub == uc;
-        if (whole) {
+    }
+    const uint32_t ib = stage_acquire(inbox) + (uint32_t)((gi & 1) * SP * S) * 512u;
+    for (int it = threadIdx.x; it < SP * 32; it += blockDim.x) {
+      const int pn = it >> 5, ln = it & 31, pi = gi * SP + pn;
+      if (pi >= np || leader_of(pn) != r) continue;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r2 = 0; r2 < S; ++r2) {
+        const float4 v = lds128f(ib + (uint32_t)((pn * S + r2) * 32 + ln) * 16u);
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+      }
+      frag_write(a, pa + pi, ln, sum);
+    }
+  };
+
+  const int ngroups = (np + SP - 1) / SP;
+  uint32_t c_slot = ring;
+  for (int gi = 0; gi < ngroups; ++gi) {
+    float acc[kFragGroup][4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const long long n = (long long)p * kFragRows + g + ((e & 2) ? 8 : 0);
-            const int m = 2 * t + (e & 1);
-            if (n < a.N && m < a.M) {
-              const __half h = __float2half_rn(sum[e]);
-              if (a.out_transposed) a.y[n * a.ldy + m] = h;
-              else a.y[(long long)m * a.ldy + n] = h;
-            }
-          }
+    for (int k = 0; k < kFragGroup; ++k) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kFragGroup; ++k) {
+      if (k < SPW && gi * SP + k * PP + wp < np) {
+        uint32_t xq = xf;
+        for (int qi = 0; qi < per; ++qi) {
+          cp_async_wait<kFragRing - 2>();  // this slot has landed (the younger ones may still be in flight)
+          __syncwarp();                    // ... for every lane, and every lane is done with the previous slot
+          fetch();                         // refill the previous slot
+          Fmt::template unit<MODE>(acc[k], a, stage_acquire(c_slot), xq, g, t, lane);
+          values_ready(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+          xq += (uint32_t)Wu * Fmt::kXBytes;
+          c_slot += kStride;
+          if (c_slot == ring_end) c_slot = ring;
+        }
+        if (MODE == 1) {
+          // single activation row: each lane holds partial dot products of rows g (acc[0]) and
+          // g + 8 (acc[2]) over its own k positions; add across the four lanes of a row
+          float &a0 = acc[k][0], &a2 = acc[k][2];
+          a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
+          a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
+          a2 += __shfl_xor_sync(0xffffffffu, a2, 1);
+          a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
+          if (t != 0) a0 = a2 = 0.f;  // one copy per row enters the sums below (column m = 0)
+          acc[k][1] = acc[k][3] = 0.f;
+        }
+      }
+    }
+
+    // add the warps' partial tiles (all threads, one output element each)
+    __syncthreads();  // the previous group's readers are done with the buffer
+#pragma unroll
+    for (int k = 0; k < kFragGroup; ++k)
+      if (k < SPW) sts128(red + ((uint32_t)(warp * SPW + k) * 32u + lane) * 16u, make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]));
+    __syncthreads();
+    if (S > 1 && gi > 0) {
+      cluster_wait_relaxed();  // every CTA has read what it led of group gi - 2: that inbox half is free
+      finish_group(gi - 1);
+    }
+    if (S > 1 && threadIdx.x == 0) {
+      // what this CTA will receive for group gi: S partial panels for every panel it leads
+      int led = 0;
+      for (int pn = 0; pn < SP; ++pn) led += (gi * SP + pn < np && leader_of(pn) == r) ? 1 : 0;
+      mbar_arrive_expect_tx(full_p + (gi & 1), (uint32_t)(led * S) * 512u);
+    }
+    {
+      const uint32_t rbs = stage_acquire(red);
+      for (int it = threadIdx.x; it < SP * 32; it += blockDim.x) {
+        const int pn = it >> 5, ln = it & 31, pi = gi * SP + pn;
+        if (pi >= np) continue;
+        const uint32_t src = rbs + (uint32_t)((((pn & (PP - 1)) * Wu * SPW + (pn >> pp_shift)) * 32 + ln) * 16);
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int w2 = 0; w2 < Wu; ++w2) {
+          const float4 v = lds128f(src + (uint32_t)(w2 * SPW) * 512u);
+          sum.x += v.x;
+          sum.y += v.y;
+          sum.z += v.z;
+          sum.w += v.w;
+        }
+        if (S == 1) {
+          frag_write(a, pa + pi, ln, sum);
         } else {
-          // park the partial tile; it is committed after the loop
-          long long jf;
-          frag_touch(p, c, a.units, a.S, a.P, a.Gc, &jf);
-          const int slot = jf < 0 ? ua : (int)(j - jf);
-          float *sl = a.scratch + (((long long)p * a.S + c) * a.SL + slot) * 128;
-          __stcg(reinterpret_cast<float4 *>(sl) + lane, make_float4(sum[0], sum[1], sum[2], sum[3]));
+          const uint32_t lead = (uint32_t)leader_of(pn);
+          const uint32_t mine = inbox + (uint32_t)(((((gi & 1) * SP + pn) * S + r) * 32 + ln) * 16);
+          st_async128(cluster_map(mine, lead), sum, cluster_map(full + (uint32_t)(gi & 1) * 8u, lead));
         }
       }
     }
-
-    // deferred commit of the panels this warp finished that were shared with other CTAs
-    __threadfence();
-    for (int pi = warp; pi < npanels; pi += W) {
-      const int p = pa + pi;
-      const int ua = (p == pa) ? ua_first : 0, ub = (p == pb) ? ub_last : uc;
-      if (a.S == 1 && ua == 0 && ub == uc) continue;
-      int expected = 0;
-      for (int c2 = 0; c2 < a.S; ++c2) expected += frag_touch(p, c2, a.units, a.S, a.P, a.Gc, nullptr);
-      unsigned int old = 0;
-      if (lane == 0) old = atomicAdd(&a.counters[p], 1u);
-      old = __shfl_sync(0xffffffffu, old, 0);
-      if ((int)old != expected - 1) continue;
-      __threadfence();
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int c2 = 0; c2 < a.S; ++c2) {
-        const int cnt = frag_touch(p, c2, a.units, a.S, a.P, a.Gc, nullptr);
-        for (int i = 0; i < cnt; ++i) {
-          const float *s2 = a.scratch + (((long long)p * a.S + c2) * a.SL + i) * 128;
-          const float4 v = __ldcg(reinterpret_cast<const float4 *>(s2) + lane);
-          sum[0] += v.x;
-          sum[1] += v.y;
-          sum[2] += v.z;
-          sum[3] += v.w;
-        }
-      }
-      if (lane == 0) a.counters[p] = 0u;  // ready for the next launch on this stream
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const long long n = (long long)p * kFragRows + g + ((e & 2) ? 8 : 0);
-        const int m = 2 * t + (e & 1);
-        if (n < a.N && m < a.M) {
-          const __half h = __float2half_rn(sum[e]);
-          if (a.out_transposed) a.y[n * a.ldy + m] = h;
-          else a.y[(long long)m * a.ldy + n] = h;
-        }
-      }
+    if (S > 1) cluster_arrive_relaxed();
+  }
+  if (S > 1) {
+    if (ngroups > 0) {
+      cluster_wait_relaxed();
+      finish_group(ngroups - 1);
     }
+    // no CTA leaves while another may still send to it or read its barriers
+    cluster_arrive_relaxed();
+    cluster_wait_relaxed();
   }
   cp_async_wait<0>();
 }
