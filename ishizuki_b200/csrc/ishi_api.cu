@@ -424,6 +424,7 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   const int tile_bytes = FragQ4K::kTileBytes;
   const int units = (int)(d.k / 256);
   const int P = (int)((d.n + kFragRows - 1) / kFragRows);
+  if ((long long)P * (ctx->sm_count + 1) >= (1ll << 31)) return false;  // the kernel deals panels in 32-bit arithmetic
   const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
   const char *force = getenv("ISHI_FRAG_PLAN");  // "S,per,PP" for tuning runs
   int fs = 0, fper = 0, fpp = 0;
@@ -485,27 +486,32 @@ ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weigh
 }
 
 template <class Fmt, int MODE>
-ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args, cudaStream_t st) {
+ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args, bool early, cudaStream_t st) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)(pl.NC * pl.S), 1, 1);
   cfg.blockDim = dim3((unsigned)(pl.Wu * pl.PP * 32), 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = st;
-  cudaLaunchAttribute at;
-  at.id = cudaLaunchAttributeClusterDimension;
-  at.val.clusterDim.x = (unsigned)pl.S;
-  at.val.clusterDim.y = 1;
-  at.val.clusterDim.z = 1;
-  cfg.attrs = &at;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)pl.S;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  // Programmatic dependent launch: the kernel may start while the one before it on the stream
+  // drains. It prefetches weight tiles, which no earlier kernel writes, and waits for the earlier
+  // kernels before it touches x or y. Only for projections, whose tiles were made at create.
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = early ? 2 : 1;
   ISHI_CUDA(ctx, cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, MODE>, args));
   return ISHI_OK;
 }
 
 // rows 1...16 through the warp-level kernel; gemv picks the CUDA-core variant for a single row
 ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, const ishi_weight_desc &d, const void *x,
-                     int rows, void *y, long long ldy, int flags, bool gemv, cudaStream_t st) {
+                     int rows, void *y, long long ldy, int flags, bool gemv, bool early, cudaStream_t st) {
   for (int r0 = 0; r0 < rows; r0 += 8) {
     FragArgs a;
     memset(&a, 0, sizeof(a));
@@ -530,7 +536,8 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.group_size = d.group_size;
     a.scale_dtype = d.scale_dtype;
     a.err = ctx->err_dev;
-    ishi_status s = (gemv && rows == 1) ? launch_frag<FragQ4K, 1>(ctx, pl, a, st) : launch_frag<FragQ4K, 0>(ctx, pl, a, st);
+    ishi_status s = (gemv && rows == 1) ? launch_frag<FragQ4K, 1>(ctx, pl, a, early, st)
+                                        : launch_frag<FragQ4K, 0>(ctx, pl, a, early, st);
     if (s != ISHI_OK) return s;
   }
   return ISHI_OK;
@@ -557,7 +564,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
     if (s != ISHI_OK) return s;
     s = tile_weight_frag(ctx, fp, d, ctx->ws.tiles, st);
     if (s != ISHI_OK) return s;
-    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, st);
+    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, false, st);
   }
   RowPlan pl;
   if (!make_row_plan(ctx, d, &pl)) return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
@@ -592,7 +599,9 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   const int64_t need_ld = (flags & ISHI_OUT_TRANSPOSED) ? rows : p->d.n;
   if (ldy < need_ld) return fail(ctx, ISHI_E_SHAPE, "ldy %lld shorter than %lld", (long long)ldy, (long long)need_ld);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
-  if (p->frag.ok) return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, ctx->route == ISHI_ROUTE_GEMV, st);
+  if (p->frag.ok)
+    return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, ctx->route == ISHI_ROUTE_GEMV,
+                    getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, st);
   return run_rows(ctx, p->plan, p->ws, p->fmt, p->d, x, rows, y, ldy, flags, st);
 }
 

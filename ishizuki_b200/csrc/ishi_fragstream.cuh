@@ -75,16 +75,17 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-// 16 bytes into another CTA's shared memory; the bytes count as completed on that CTA's mbarrier
+// 4 bytes into another CTA's shared memory; the bytes count as completed on that CTA's mbarrier
 // when they have landed, so the reader needs no fence: it waits for the barrier's phase
-__device__ __forceinline__ void st_async128(uint32_t addr, float4 v, uint32_t mbar) {
-  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1,%2,%3,%4}, [%5];" ::"r"(addr),
-               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(mbar)
+__device__ __forceinline__ void st_async32(uint32_t addr, float v, uint32_t mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(addr), "f"(v),
+               "r"(mbar)
                : "memory");
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// the execution barrier alone: no fence, so nothing waits for the copies and stores in flight
+// arrival without the release fence, which would wait for every copy and store in flight; the
+// data that crosses CTAs here is published by mbarriers instead
 __device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait_relaxed() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
@@ -109,20 +110,33 @@ __host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, i
          (size_t)W * kFragRing * frag_ring_stride(tile_bytes);
 }
 
-// the four accumulator registers of lane ln (g = ln / 4, t = ln % 4) of panel p: register e is
-// weight row g + 8 * (e / 2), activation row 2t + e % 2
-__device__ __forceinline__ void frag_write(const FragArgs &a, int p, int ln, float4 v) {
-  const float r[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const long long n = (long long)p * kFragRows + (ln >> 2) + ((e & 2) ? 8 : 0);
-    const int m = 2 * (ln & 3) + (e & 1);
-    if (n < a.N && m < a.M) {
-      const __half h = __float2half_rn(r[e]);
-      if (a.out_transposed) a.y[n * a.ldy + m] = h;
-      else a.y[(long long)m * a.ldy + n] = h;
-    }
+// element idx of panel p in accumulator-fragment order: lane idx / 4 (g = lane / 4, t = lane % 4),
+// register e = idx % 4 -> weight row g + 8 * (e / 2), activation row 2t + e % 2
+__device__ __forceinline__ void frag_write(const FragArgs &a, int p, int idx, float v) {
+  const int ln = idx >> 2, e = idx & 3;
+  const long long n = (long long)p * kFragRows + (ln >> 2) + ((e & 2) ? 8 : 0);
+  const int m = 2 * (ln & 3) + (e & 1);
+  if (n < a.N && m < a.M) {
+    const __half h = __float2half_rn(v);
+    if (a.out_transposed) a.y[n * a.ldy + m] = h;
+    else a.y[(long long)m * a.ldy + n] = h;
   }
+}
+
+// sum of n floats at addr, addr + stride, ...: the loads of a batch are issued together
+__device__ __forceinline__ float lds_sum(uint32_t addr, uint32_t stride, int n) {
+  float sum = 0.f;
+  int i = 0;
+  for (; i + 4 <= n; i += 4) {
+    const float v0 = lds32f(addr), v1 = lds32f(addr + stride), v2 = lds32f(addr + 2 * stride), v3 = lds32f(addr + 3 * stride);
+    sum += (v0 + v1) + (v2 + v3);
+    addr += 4 * stride;
+  }
+  for (; i < n; ++i) {
+    sum += lds32f(addr);
+    addr += stride;
+  }
+  return sum;
 }
 
 // MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row.
@@ -151,10 +165,14 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   const int cid = blockIdx.x / S;
   const int ub0 = frag_column_begin(r, a.units, S);
   const int uc = frag_column_begin(r + 1, a.units, S) - ub0;
-  const int pa = (int)(((long long)cid * a.P) / a.NC);
-  const int np = (int)(((long long)(cid + 1) * a.P) / a.NC) - pa;  // the cluster's panels: pa .. pa + np - 1
+  // the cluster's panels: pa .. pa + np - 1 (the host checks that P * NC fits 31 bits)
+  const int pa = (int)(((unsigned)cid * (unsigned)a.P) / (unsigned)a.NC);
+  const int np = (int)(((unsigned)(cid + 1) * (unsigned)a.P) / (unsigned)a.NC) - pa;
   const int per = (uc - 1 - wu + Wu) / Wu;                         // units of a panel this warp owns: wu + i * Wu < uc
   const int npw = np > wp ? (np - wp + PP - 1) / PP : 0;           // panels this warp takes: wp, wp + PP, ...
+
+  // Let the next kernel on the stream start its own prologue as SMs fall free.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // Shared memory of another CTA may be written only once that CTA runs and has set up its
   // barriers: every CTA arrives here, and waits before the first group.
@@ -165,7 +183,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       *abort_word = 0;
       mbar_fence_init();
     }
-    cluster_arrive();
+    cluster_arrive_relaxed();  // the init fence above is what the peers need; nothing else to publish yet
   }
 
   // This warp's tile sequence: its panels in order, in each its units wu + qi * Wu. The fetch
@@ -195,13 +213,18 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
 #pragma unroll
   for (int i = 0; i < kFragRing - 1; ++i) fetch();
 
+  // Everything above reads only the weight tiles. x may be the output of the kernel before this
+  // one and y may still be read by it: wait for the earlier kernels (returns at once unless this
+  // kernel was launched early).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
   // activations of the column range into fragment order (all warps), while the first tiles fly
   Fmt::stage_x(a, xfrag, ub0, uc);
   __syncthreads();
   // shared-memory loads are plain asm the compiler may move; tie their addresses to the waits
   const uint32_t xf = stage_acquire(xfrag) + (uint32_t)wu * Fmt::kXBytes;
 
-  if (S > 1) cluster_wait();
+  if (S > 1) cluster_wait_relaxed();
 
   // the leader of a group's panel pn: rank pn % S
   auto leader_of = [&](int pn) -> int { return pn - ((pn * a.inv_s) >> 16) * S; };
@@ -221,18 +244,10 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       }
     }
     const uint32_t ib = stage_acquire(inbox) + (uint32_t)((gi & 1) * SP * S) * 512u;
-    for (int it = threadIdx.x; it < SP * 32; it += blockDim.x) {
-      const int pn = it >> 5, ln = it & 31, pi = gi * SP + pn;
+    for (int f = threadIdx.x; f < SP * 128; f += blockDim.x) {
+      const int pn = f >> 7, idx = f & 127, pi = gi * SP + pn;
       if (pi >= np || leader_of(pn) != r) continue;
-      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r2 = 0; r2 < S; ++r2) {
-        const float4 v = lds128f(ib + (uint32_t)((pn * S + r2) * 32 + ln) * 16u);
-        sum.x += v.x;
-        sum.y += v.y;
-        sum.z += v.z;
-        sum.w += v.w;
-      }
-      frag_write(a, pa + pi, ln, sum);
+      frag_write(a, pa + pi, idx, lds_sum(ib + (uint32_t)(pn * S * 128 + idx) * 4u, 512u, S));
     }
   };
 
@@ -282,30 +297,24 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
     }
     if (S > 1 && threadIdx.x == 0) {
       // what this CTA will receive for group gi: S partial panels for every panel it leads
-      int led = 0;
-      for (int pn = 0; pn < SP; ++pn) led += (gi * SP + pn < np && leader_of(pn) == r) ? 1 : 0;
+      // (panels r, r + S, ... of the group, as far as the group goes)
+      const int left = min(SP, np - gi * SP);
+      const int led = left > r ? (left - r + S - 1) / S : 0;
       mbar_arrive_expect_tx(full_p + (gi & 1), (uint32_t)(led * S) * 512u);
     }
     {
       const uint32_t rbs = stage_acquire(red);
-      for (int it = threadIdx.x; it < SP * 32; it += blockDim.x) {
-        const int pn = it >> 5, ln = it & 31, pi = gi * SP + pn;
+      for (int f = threadIdx.x; f < SP * 128; f += blockDim.x) {
+        const int pn = f >> 7, idx = f & 127, pi = gi * SP + pn;
         if (pi >= np) continue;
-        const uint32_t src = rbs + (uint32_t)((((pn & (PP - 1)) * Wu * SPW + (pn >> pp_shift)) * 32 + ln) * 16);
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int w2 = 0; w2 < Wu; ++w2) {
-          const float4 v = lds128f(src + (uint32_t)(w2 * SPW) * 512u);
-          sum.x += v.x;
-          sum.y += v.y;
-          sum.z += v.z;
-          sum.w += v.w;
-        }
+        const uint32_t src = rbs + (uint32_t)(((pn & (PP - 1)) * Wu * SPW + (pn >> pp_shift)) * 128 + idx) * 4u;
+        const float sum = lds_sum(src, (uint32_t)SPW * 512u, Wu);
         if (S == 1) {
-          frag_write(a, pa + pi, ln, sum);
+          frag_write(a, pa + pi, idx, sum);
         } else {
           const uint32_t lead = (uint32_t)leader_of(pn);
-          const uint32_t mine = inbox + (uint32_t)(((((gi & 1) * SP + pn) * S + r) * 32 + ln) * 16);
-          st_async128(cluster_map(mine, lead), sum, cluster_map(full + (uint32_t)(gi & 1) * 8u, lead));
+          const uint32_t mine = inbox + (uint32_t)((((gi & 1) * SP + pn) * S + r) * 128 + idx) * 4u;
+          st_async32(cluster_map(mine, lead), sum, cluster_map(full + (uint32_t)(gi & 1) * 8u, lead));
         }
       }
     }
