@@ -38,6 +38,11 @@ ROWS = 8
 METRIC = "quantized-matmul weight GB/s (% of HBM peak) at M=1/8 draft rows; µs/layer"
 
 
+# dram__bytes read + written per launch of the product kernel, from the ncu capture summarised in
+# profiles/frag_kernel_q4k_mlp_m8.md (mean of gate, up, down: 50.28, 50.28, 50.49 MB)
+NCU_DRAM_BYTES_PER_LAUNCH = 50.35e6
+
+
 def weight_bytes(n: int, k: int) -> int:
     return n * (k // 256) * 144
 
@@ -296,7 +301,8 @@ def run_ours(args) -> dict | None:
         "us_per_layer": ms_per_step * 1e3 / layers,
         "pct_of_hbm_peak": {"measured_%d" % int(peak): 100.0 * value / world / peak, "nominal_8000": 100.0 * value / world / 8000.0},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": "rowstream_kernel<RowQ4K>", "peak_kind": peak_kind},
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
+                     "kernel": "frag_kernel<FragQ4K, 0>", "peak_kind": peak_kind},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
