@@ -424,7 +424,8 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   const int tile_bytes = FragQ4K::kTileBytes;
   const int units = (int)(d.k / 256);
   const int P = (int)((d.n + kFragRows - 1) / kFragRows);
-  if ((long long)P * (ctx->sm_count + 1) >= (1ll << 31)) return false;  // the kernel deals panels in 32-bit arithmetic
+  // the kernel divides by multiplication, exact while (clusters + 1) * P < 2^32 / clusters
+  if ((long long)P * (ctx->sm_count + 1) * ctx->sm_count >= (1ll << 32)) return false;
   const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
   const char *force = getenv("ISHI_FRAG_PLAN");  // "S,per,PP" for tuning runs
   int fs = 0, fper = 0, fpp = 0;
@@ -457,7 +458,9 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
         if (c.NC < 1) continue;
         const int panels = (P + c.NC - 1) / c.NC;
         const double tile_time = std::max(1.0, w / 12.0) * (1.0 + 2.0 / w);  // issue-bound past ~12 warps; few warps hide less latency
-        c.cost = (double)((panels + pp - 1) / pp) * per * tile_time + 0.05 * umax + 0.5 / c.SPW;
+        const int rounds = (panels + pp - 1) / pp;                 // panels one warp walks
+        const int groups = (rounds + c.SPW - 1) / c.SPW;            // ... and reductions it takes part in
+        c.cost = (double)rounds * per * tile_time + groups * (0.3 + 0.03 * wu) + 0.05 * umax;
         c.ok = true;
         if (!best.ok || c.cost < best.cost) best = c;
       }
@@ -531,7 +534,9 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.PP = pl.PP;
     a.SPW = pl.SPW;
     a.pp_shift = pl.PP == 4 ? 2 : pl.PP == 2 ? 1 : 0;
-    a.inv_s = (65536 + pl.S - 1) / pl.S;
+    a.inv_s = frag_inverse(pl.S);
+    a.inv_nc = frag_inverse(pl.NC);
+    a.inv_wu = frag_inverse(pl.Wu);
     a.umax = pl.umax;
     a.group_size = d.group_size;
     a.scale_dtype = d.scale_dtype;

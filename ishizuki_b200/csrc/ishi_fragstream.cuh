@@ -47,7 +47,8 @@ struct FragArgs {
   int units, S, P, NC;  // NC clusters of S CTAs
   int Wu, PP, SPW;      // warps per panel, panels in parallel (1, 2 or 4; Wu * PP warps per CTA), panels per warp and group
   int pp_shift;         // log2(PP)
-  int inv_s;            // ceil(65536 / S): n / S = (n * inv_s) >> 16 for n < 8192
+  // ceil(2^32 / d) for d = S, NC, Wu, or 0 for d = 1: see frag_div()
+  unsigned inv_s, inv_nc, inv_wu;
   int umax;             // most units in a column range
   int group_size, scale_dtype;
   int *err;             // raised when a bounded wait gives up
@@ -64,9 +65,10 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
+// (not volatile: callers tie the address to the barrier that publishes the data)
 __device__ __forceinline__ float lds32f(uint32_t addr) {
   float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
   return v;
 }
 // the address of this CTA's shared-memory location addr in CTA rank of the cluster
@@ -100,6 +102,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 
+// n / d through inv = ceil(2^32 / d), exact for n * d < 2^32; inv = 0 stands for d = 1
+__device__ __forceinline__ int frag_div(unsigned n, unsigned inv) { return inv ? (int)__umulhi(n, inv) : (int)n; }
+__host__ inline unsigned frag_inverse(int d) { return d == 1 ? 0u : (unsigned)(((1ull << 32) + d - 1) / d); }
+
 __host__ __device__ inline int frag_column_begin(int c, int units, int S) { return (c * units) / S; }
 __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_bytes + 127) & ~127; }
 
@@ -123,20 +129,17 @@ __device__ __forceinline__ void frag_write(const FragArgs &a, int p, int idx, fl
   }
 }
 
-// sum of n floats at addr, addr + stride, ...: the loads of a batch are issued together
+// sum of n <= kFragMaxWarps floats at addr, addr + stride, ...: all loads are issued before the
+// first add, so the latency of shared memory is paid once
 __device__ __forceinline__ float lds_sum(uint32_t addr, uint32_t stride, int n) {
-  float sum = 0.f;
-  int i = 0;
-  for (; i + 4 <= n; i += 4) {
-    const float v0 = lds32f(addr), v1 = lds32f(addr + stride), v2 = lds32f(addr + 2 * stride), v3 = lds32f(addr + 3 * stride);
-    sum += (v0 + v1) + (v2 + v3);
-    addr += 4 * stride;
-  }
-  for (; i < n; ++i) {
-    sum += lds32f(addr);
-    addr += stride;
-  }
-  return sum;
+  float v[kFragMaxWarps];
+#pragma unroll
+  for (int i = 0; i < kFragMaxWarps; ++i) v[i] = i < n ? lds32f(addr + (uint32_t)i * stride) : 0.f;
+#pragma unroll
+  for (int w = 1; w < kFragMaxWarps; w *= 2)
+#pragma unroll
+    for (int i = 0; i + w < kFragMaxWarps; i += 2 * w) v[i] += v[i + w];
+  return v[0];
 }
 
 // MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row.
@@ -150,7 +153,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   const int g = lane >> 2, t = lane & 3;
   const int S = a.S, Wu = a.Wu, PP = a.PP, SPW = a.SPW, pp_shift = a.pp_shift;
   const int W = Wu * PP, SP = SPW * PP;
-  const int wu = warp % Wu, wp = warp / Wu;  // this warp's unit lane and panel lane
+  const int wp = frag_div((unsigned)warp, a.inv_wu), wu = warp - wp * Wu;  // this warp's panel lane and unit lane
 
   const uint32_t xfrag = smem_u32(smem);                          // [umax][Fmt::kXBytes]
   const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;   // [W][SPW][128 floats]
@@ -161,15 +164,16 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   volatile int *abort_word = reinterpret_cast<volatile int *>(full_p + 2);
   const uint32_t ring_end = ring + kFragRing * kStride;
 
-  const int r = blockIdx.x % S;  // rank in the cluster = column range
-  const int cid = blockIdx.x / S;
-  const int ub0 = frag_column_begin(r, a.units, S);
-  const int uc = frag_column_begin(r + 1, a.units, S) - ub0;
-  // the cluster's panels: pa .. pa + np - 1 (the host checks that P * NC fits 31 bits)
-  const int pa = (int)(((unsigned)cid * (unsigned)a.P) / (unsigned)a.NC);
-  const int np = (int)(((unsigned)(cid + 1) * (unsigned)a.P) / (unsigned)a.NC) - pa;
-  const int per = (uc - 1 - wu + Wu) / Wu;                         // units of a panel this warp owns: wu + i * Wu < uc
-  const int npw = np > wp ? (np - wp + PP - 1) / PP : 0;           // panels this warp takes: wp, wp + PP, ...
+  // (divisions by multiplication: the host checks the ranges)
+  const int cid = frag_div(blockIdx.x, a.inv_s);
+  const int r = (int)blockIdx.x - cid * S;  // rank in the cluster = column range
+  const int ub0 = frag_div((unsigned)(r * a.units), a.inv_s);  // = frag_column_begin(r, units, S)
+  const int uc = frag_div((unsigned)((r + 1) * a.units), a.inv_s) - ub0;
+  // the cluster's panels: pa .. pa + np - 1
+  const int pa = frag_div((unsigned)cid * (unsigned)a.P, a.inv_nc);
+  const int np = frag_div((unsigned)(cid + 1) * (unsigned)a.P, a.inv_nc) - pa;
+  const int per = frag_div((unsigned)(uc - 1 - wu + Wu), a.inv_wu);  // units of a panel this warp owns: wu + i * Wu < uc
+  const int npw = np > wp ? (np - wp + PP - 1) >> pp_shift : 0;           // panels this warp takes: wp, wp + PP, ...
 
   // Let the next kernel on the stream start its own prologue as SMs fall free.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -189,16 +193,16 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   // This warp's tile sequence: its panels in order, in each its units wu + qi * Wu. The fetch
   // cursor runs kFragRing - 1 tiles ahead of the compute cursor.
   int f_left = npw * per, f_qi = 0;
-  uint32_t f_slot = ring;
-  const uint8_t *f_src = a.tiles + ((long long)(pa + wp) * a.units + ub0 + wu) * (long long)kTile;
+  uint32_t f_slot = ring + (uint32_t)lane * 16u;  // this lane's 16 bytes of every 512
+  const uint32_t f_end = ring_end + (uint32_t)lane * 16u;
+  const uint8_t *f_src = a.tiles + ((long long)(pa + wp) * a.units + ub0 + wu) * (long long)kTile + lane * 16;
   const long long step_unit = (long long)Wu * kTile;
   const long long step_panel = ((long long)PP * a.units - (long long)per * Wu) * kTile;
   auto fetch = [&]() {
     if (f_left > 0) {
 #pragma unroll
-      for (int o = 0; o + 512 <= kTile; o += 512) cp_async16(f_slot + o + lane * 16, f_src + o + lane * 16);
-      if ((kTile & 511) != 0 && lane * 16 < (kTile & 511))
-        cp_async16(f_slot + (kTile & ~511) + lane * 16, f_src + (kTile & ~511) + lane * 16);
+      for (int o = 0; o + 512 <= kTile; o += 512) cp_async16(f_slot + o, f_src + o);
+      if ((kTile & 511) != 0 && lane * 16 < (kTile & 511)) cp_async16(f_slot + (kTile & ~511), f_src + (kTile & ~511));
     }
     cp_async_commit();  // one group per slot, present or not, so the wait below counts slots
     --f_left;
@@ -208,7 +212,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       f_src += step_panel;
     }
     f_slot += kStride;
-    if (f_slot == ring_end) f_slot = ring;
+    if (f_slot == f_end) f_slot -= kFragRing * kStride;
   };
 #pragma unroll
   for (int i = 0; i < kFragRing - 1; ++i) fetch();
@@ -227,7 +231,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   if (S > 1) cluster_wait_relaxed();
 
   // the leader of a group's panel pn: rank pn % S
-  auto leader_of = [&](int pn) -> int { return pn - ((pn * a.inv_s) >> 16) * S; };
+  auto leader_of = [&](int pn) -> int { return pn - frag_div((unsigned)pn, a.inv_s) * S; };
   // the leaders' part of group gi: wait for the S partial panels, add them in rank order, write y
   auto finish_group = [&](int gi) {
     const uint32_t bar = full + (uint32_t)(gi & 1) * 8u, parity = (uint32_t)(gi >> 1) & 1u;
