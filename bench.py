@@ -224,6 +224,9 @@ def run_ours(args) -> dict | None:
     with torch.cuda.stream(stream):
         one_pass()
         torch.cuda.synchronize()
+        # One CUDA graph per step on one GPU. With NCCL all-gathers in the step the launches stay
+        # eager: capturing them together with the early-launched product kernels did not finish
+        # within ten minutes when tried at two ranks, cause not established.
         if world == 1:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
