@@ -258,19 +258,18 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   const int ngroups = (np + SP - 1) / SP;
   uint32_t c_slot = ring;
   for (int gi = 0; gi < ngroups; ++gi) {
-    float acc[kFragGroup][4];
-#pragma unroll
-    for (int k = 0; k < kFragGroup; ++k) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f;
-#pragma unroll
-    for (int k = 0; k < kFragGroup; ++k) {
-      if (k < SPW && gi * SP + k * PP + wp < np) {
+    // this warp's panels of the group, one after the other; each partial tile goes straight to the
+    // reduction buffer (the barrier at the end of the previous group freed it)
+    for (int k = 0; k < SPW; ++k) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (gi * SP + k * PP + wp < np) {
         uint32_t xq = xf;
         for (int qi = 0; qi < per; ++qi) {
           cp_async_wait<kFragRing - 2>();  // this slot has landed (the younger ones may still be in flight)
           __syncwarp();                    // ... for every lane, and every lane is done with the previous slot
           fetch();                         // refill the previous slot
-          Fmt::template unit<MODE>(acc[k], a, stage_acquire(c_slot), xq, g, t, lane);
-          values_ready(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+          Fmt::template unit<MODE>(acc, a, stage_acquire(c_slot), xq, g, t, lane);
+          values_ready(acc[0], acc[1], acc[2], acc[3]);
           xq += (uint32_t)Wu * Fmt::kXBytes;
           c_slot += kStride;
           if (c_slot == ring_end) c_slot = ring;
@@ -278,22 +277,18 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
         if (MODE == 1) {
           // single activation row: each lane holds partial dot products of rows g (acc[0]) and
           // g + 8 (acc[2]) over its own k positions; add across the four lanes of a row
-          float &a0 = acc[k][0], &a2 = acc[k][2];
-          a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
-          a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
-          a2 += __shfl_xor_sync(0xffffffffu, a2, 1);
-          a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
-          if (t != 0) a0 = a2 = 0.f;  // one copy per row enters the sums below (column m = 0)
-          acc[k][1] = acc[k][3] = 0.f;
+          acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+          acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
+          acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 1);
+          acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 2);
+          if (t != 0) acc[0] = acc[2] = 0.f;  // one copy per row enters the sums below (column m = 0)
+          acc[1] = acc[3] = 0.f;
         }
       }
+      sts128(red + ((uint32_t)(warp * SPW + k) * 32u + lane) * 16u, make_float4(acc[0], acc[1], acc[2], acc[3]));
     }
 
     // add the warps' partial tiles (all threads, one output element each)
-    __syncthreads();  // the previous group's readers are done with the buffer
-#pragma unroll
-    for (int k = 0; k < kFragGroup; ++k)
-      if (k < SPW) sts128(red + ((uint32_t)(warp * SPW + k) * 32u + lane) * 16u, make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]));
     __syncthreads();
     if (S > 1 && gi > 0) {
       cluster_wait_relaxed();  // every CTA has read what it led of group gi - 2: that inbox half is free
@@ -323,6 +318,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       }
     }
     if (S > 1) cluster_arrive_relaxed();
+    __syncthreads();  // every thread has read the reduction buffer: the next group may write it
   }
   if (S > 1) {
     if (ngroups > 0) {
