@@ -14,6 +14,7 @@
 
 #include "../../include/ishizuki_cuda.h"
 #include "dequant.cuh"
+#include "ffmt_affine.cuh"
 #include "ffmt_q4k.cuh"
 #include "ishi_fragstream.cuh"
 #include "ishi_rowstream.cuh"
@@ -50,6 +51,7 @@ struct RowPlan {
 // Launch plan of the warp-level kernel (fragment-order tiles, 16-row panels, clusters of S CTAs).
 struct FragPlan {
   bool ok = false;
+  int fmt_id = -1;  // see frag_format()
   int units = 0, S = 1, P = 0, NC = 1, Wu = 1, PP = 1, SPW = 1, umax = 0, tile_bytes = 0;
   size_t smem = 0, tiles_bytes = 0;
   double cost = 0;
@@ -366,7 +368,32 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
 
 // ---- warp-level kernel: plan, tiling, launch ------------------------------------------------------
 
-bool has_frag_kernel(int fmt) { return fmt == ISHI_GGML_Q4_K; }
+// Which fragment decoder serves a weight, or -1 (the tcgen05 kernel then takes it).
+int frag_format(const ishi_weight_desc &d) {
+  if (d.kind == ISHI_KIND_GGML) return d.ggml_type == ISHI_GGML_Q4_K ? 0 : -1;
+  if (d.scale_dtype != ISHI_DT_F16 && d.scale_dtype != ISHI_DT_BF16) return -1;
+  if (d.bits == 4) return d.group_size == 32 ? 1 : d.group_size == 64 ? 2 : d.group_size == 128 ? 3 : -1;
+  if (d.bits == 2) return d.group_size == 64 ? 4 : d.group_size == 128 ? 5 : -1;
+  return -1;
+}
+
+template <class T>
+struct FragTag {
+  typedef T type;
+};
+
+// calls f(FragTag<decoder>) for the decoder of fmt_id
+template <class F>
+auto with_frag_format(int fmt_id, F &&f) {
+  switch (fmt_id) {
+    case 1: return f(FragTag<FragAffine<4, 32>>());
+    case 2: return f(FragTag<FragAffine<4, 64>>());
+    case 3: return f(FragTag<FragAffine<4, 128>>());
+    case 4: return f(FragTag<FragAffine<2, 64>>());
+    case 5: return f(FragTag<FragAffine<2, 128>>());
+    default: return f(FragTag<FragQ4K>());
+  }
+}
 
 template <class Fmt, int MODE>
 ishi_status configure_frag(ishi_ctx *ctx) {
@@ -382,12 +409,13 @@ ishi_status configure_frag(ishi_ctx *ctx) {
 }
 
 // how many clusters of s CTAs with this much shared memory the device runs at once
-int max_frag_clusters(ishi_ctx *ctx, int s, int warps, size_t smem) {
+template <class Fmt>
+int max_frag_clusters(ishi_ctx *ctx, int fmt_id, int s, int warps, size_t smem) {
   if (s == 1) return ctx->sm_count;
-  static std::map<std::tuple<int, int, int, size_t>, int> cache;
+  static std::map<std::tuple<int, int, int, int, size_t>, int> cache;
   static std::mutex lock;
   std::lock_guard<std::mutex> g(lock);
-  const auto key = std::make_tuple(ctx->device, s, warps, smem);
+  const auto key = std::make_tuple(ctx->device, fmt_id, s, warps, smem);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
   cudaLaunchConfig_t cfg;
@@ -403,7 +431,7 @@ int max_frag_clusters(ishi_ctx *ctx, int s, int warps, size_t smem) {
   cfg.attrs = &at;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, frag_kernel<FragQ4K, 0>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, frag_kernel<Fmt, 0>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     n = 0;
   }
@@ -415,13 +443,12 @@ int max_frag_clusters(ishi_ctx *ctx, int s, int warps, size_t smem) {
 // parallel and the panels per group. The estimate counts tile times on the longest warp (panels of
 // the fullest cluster x units per warp), stretched where the warps outnumber what the issue slots
 // sustain.
-bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
-  const int fmt = format_of(d);
-  if (!has_frag_kernel(fmt)) return false;
-  if (configure_frag<FragQ4K, 0>(ctx) != ISHI_OK || configure_frag<FragQ4K, 1>(ctx) != ISHI_OK) return false;
-  const int xbytes = FragQ4K::kXBytes;
+template <class Fmt>
+bool make_frag_plan_for(ishi_ctx *ctx, const ishi_weight_desc &d, int fmt_id, FragPlan *pl) {
+  if (configure_frag<Fmt, 0>(ctx) != ISHI_OK || configure_frag<Fmt, 1>(ctx) != ISHI_OK) return false;
+  const int xbytes = Fmt::kXBytes;
   FragPlan best;
-  const int tile_bytes = FragQ4K::kTileBytes;
+  const int tile_bytes = Fmt::kTileBytes;
   const int units = (int)(d.k / 256);
   const int P = (int)((d.n + kFragRows - 1) / kFragRows);
   // the kernel divides by multiplication, exact while (clusters + 1) * P < 2^32 / clusters
@@ -454,7 +481,7 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
         }
         if (c.SPW < 1) continue;
         // one CTA per SM: two would stage the activations twice and split the issue slots
-        c.NC = std::min(std::min(max_frag_clusters(ctx, s, w, c.smem), ctx->sm_count / s), P);
+        c.NC = std::min(std::min(max_frag_clusters<Fmt>(ctx, fmt_id, s, w, c.smem), ctx->sm_count / s), P);
         if (c.NC < 1) continue;
         const int panels = (P + c.NC - 1) / c.NC;
         const double tile_time = std::max(1.0, w / 12.0) * (1.0 + 2.0 / w);  // issue-bound past ~12 warps; few warps hide less latency
@@ -468,6 +495,7 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   }
   if (!best.ok) return false;
   best.tiles_bytes = (size_t)P * units * tile_bytes;
+  best.fmt_id = fmt_id;
   if (getenv("ISHI_DEBUG_PLAN"))
     fprintf(stderr, "ishi plan n=%lld k=%lld: split %d, clusters %d, warps %d x %d, panels per warp and group %d, smem %zu\n",
             (long long)d.n, (long long)d.k, best.S, best.NC, best.Wu, best.PP, best.SPW, best.smem);
@@ -475,15 +503,35 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   return true;
 }
 
+bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
+  const int fmt_id = frag_format(d);
+  if (fmt_id < 0) return false;
+  return with_frag_format(fmt_id, [&](auto tag) {
+    return make_frag_plan_for<typename decltype(tag)::type>(ctx, d, fmt_id, pl);
+  });
+}
+
 ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weight_desc &d, uint8_t *dst, cudaStream_t st) {
   FragSrc src;
   memset(&src, 0, sizeof(src));
   src.w = static_cast<const uint8_t *>(d.weight_dev);
-  src.w_row_bytes = (long long)(d.k / 256) * type_size(d.ggml_type);
   src.N = d.n;
+  if (d.kind == ISHI_KIND_GGML) {
+    src.w_row_bytes = (long long)(d.k / 256) * type_size(d.ggml_type);
+  } else {
+    src.w_row_bytes = (long long)d.k * d.bits / 8;
+    src.scales = static_cast<const uint8_t *>(d.scales_dev);
+    src.biases = static_cast<const uint8_t *>(d.biases_dev);
+    src.group_size = d.group_size;
+    src.scale_bytes = 2;
+    src.s_row_bytes = (long long)(d.k / d.group_size) * 2;
+  }
   const long long total = (long long)pl.P * pl.units * (pl.tile_bytes / 2);
   const int grid = (int)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
-  prepare_frag_kernel<FragQ4K><<<grid, 256, 0, st>>>(src, pl.units, pl.tile_bytes, dst);
+  with_frag_format(pl.fmt_id, [&](auto tag) {
+    prepare_frag_kernel<typename decltype(tag)::type><<<grid, 256, 0, st>>>(src, pl.units, pl.tile_bytes, dst);
+    return 0;
+  });
   ISHI_CUDA(ctx, cudaGetLastError());
   return ISHI_OK;
 }
@@ -541,8 +589,11 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.group_size = d.group_size;
     a.scale_dtype = d.scale_dtype;
     a.err = ctx->err_dev;
-    ishi_status s = (gemv && rows == 1) ? launch_frag<FragQ4K, 1>(ctx, pl, a, early, st)
-                                        : launch_frag<FragQ4K, 0>(ctx, pl, a, early, st);
+    const bool single = gemv && rows == 1;
+    ishi_status s = with_frag_format(pl.fmt_id, [&](auto tag) {
+      typedef typename decltype(tag)::type Fmt;
+      return single ? launch_frag<Fmt, 1>(ctx, pl, a, early, st) : launch_frag<Fmt, 0>(ctx, pl, a, early, st);
+    });
     if (s != ISHI_OK) return s;
   }
   return ISHI_OK;

@@ -116,6 +116,11 @@ __device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
                "f"(v.w)
                : "memory");
 }
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+  float2 v;
+  asm("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ float4 lds128f(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
