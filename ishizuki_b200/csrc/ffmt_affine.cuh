@@ -93,6 +93,9 @@ struct FragAffine {
         const int i = i0 + e * nw;
         if (i >= tasks) break;
         const int g = i & 7;
+        if (a.rot_block)
+          v[e] = frag_rotate8(v[e], a.rot_block,
+                              a.rot_signs ? a.rot_signs + (long long)(ub0 + (i >> 3)) * 256 + lane * 8 : nullptr, lane);
         const uint32_t base = xfrag + (uint32_t)(i >> 3) * kXBytes;
         // halves of v: x0 x1 | x2 x3 | x4 x5 | x6 x7
         if (BITS == 4) {

@@ -69,6 +69,9 @@ struct FragQ4K {
         const int i = i0 + e * nw;
         if (i >= tasks) break;
         const int g = i & 7;
+        if (a.rot_block)
+          v[e] = frag_rotate8(v[e], a.rot_block,
+                              a.rot_signs ? a.rot_signs + (long long)(ub0 + (i >> 3)) * 256 + lane * 8 : nullptr, lane);
         const uint32_t base = xfrag + (uint32_t)(i >> 3) * kXBytes;
         const uint32_t dst = base + (uint32_t)(4 * jj + 2 * hh) * 256u + (uint32_t)(((g ^ jj) * 4 + tt) * 8);
         sts64(dst, prmt(v[e].x, v[e].y, 0x5410u), prmt(v[e].x, v[e].y, 0x7632u));

@@ -562,7 +562,7 @@ ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args,
 
 // rows 1...16 through the warp-level kernel; gemv picks the CUDA-core variant for a single row
 ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, const ishi_weight_desc &d, const void *x,
-                     int rows, void *y, long long ldy, int flags, bool gemv, bool early, cudaStream_t st) {
+                     int rows, void *y, long long ldy, int flags, bool gemv, bool early, bool rotate, cudaStream_t st) {
   for (int r0 = 0; r0 < rows; r0 += 8) {
     FragArgs a;
     memset(&a, 0, sizeof(a));
@@ -589,6 +589,8 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.group_size = d.group_size;
     a.scale_dtype = d.scale_dtype;
     a.err = ctx->err_dev;
+    a.rot_block = rotate ? d.hadamard_block : 0;
+    a.rot_signs = rotate ? static_cast<const float *>(d.signs_dev) : nullptr;
     const bool single = gemv && rows == 1;
     ishi_status s = with_frag_format(pl.fmt_id, [&](auto tag) {
       typedef typename decltype(tag)::type Fmt;
@@ -620,7 +622,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
     if (s != ISHI_OK) return s;
     s = tile_weight_frag(ctx, fp, d, ctx->ws.tiles, st);
     if (s != ISHI_OK) return s;
-    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, false, st);
+    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, false, false, st);
   }
   RowPlan pl;
   if (!make_row_plan(ctx, d, &pl)) return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
@@ -647,8 +649,15 @@ ishi_status ggml_raw(ishi_ctx *ctx, const void *x, int rows, const void *blocks,
   return raw_product(ctx, d, x, rows, y, gemv, static_cast<cudaStream_t>(stream));
 }
 
+// The warp-level kernel rotates x while it stages it when a block fits one 256-wide unit.
+bool rotates_in_kernel(const ishi_projection *p) {
+  const int b = p->d.hadamard_block;
+  return p->frag.ok && b >= 8 && b <= 256 && (b & (b - 1)) == 0;
+}
+
+// rotate: x is unrotated and the projection's rotation is applied inside the product kernel
 ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void *y, int64_t ldy, int flags,
-                              cudaStream_t st) {
+                              bool rotate, cudaStream_t st) {
   ishi_ctx *ctx = p->ctx;
   ishi_status s = check_io(ctx, x, rows, y, 16);
   if (s != ISHI_OK) return s;
@@ -657,7 +666,8 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   if (p->frag.ok)
     return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, ctx->route == ISHI_ROUTE_GEMV,
-                    getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, st);
+                    getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, rotate, st);
+  if (rotate) return fail(ctx, ISHI_E_INVALID, "in-kernel rotation asked of a kernel that has none");
   return run_rows(ctx, p->plan, p->ws, p->fmt, p->d, x, rows, y, ldy, flags, st);
 }
 
@@ -939,17 +949,20 @@ ishi_status ishi_projection_rotate(ishi_projection *p, const void *x, int rows, 
 ishi_status ishi_projection_apply_rotated(ishi_projection *p, const void *xr, int rows, void *y, int64_t ldy,
                                           int flags, void *stream) {
   if (!p) return ISHI_E_INVALID;
-  return projection_matmul(p, xr, rows, y, ldy, flags, static_cast<cudaStream_t>(stream));
+  return projection_matmul(p, xr, rows, y, ldy, flags, false, static_cast<cudaStream_t>(stream));
 }
 
 ishi_status ishi_projection_apply(ishi_projection *p, const void *x, int rows, void *y, int64_t ldy, int flags,
                                   void *stream) {
   if (!p) return ISHI_E_INVALID;
-  if (p->d.hadamard_block == 0) return projection_matmul(p, x, rows, y, ldy, flags, static_cast<cudaStream_t>(stream));
+  if (p->d.hadamard_block == 0)
+    return projection_matmul(p, x, rows, y, ldy, flags, false, static_cast<cudaStream_t>(stream));
   if (rows < 1 || rows > 16) return fail(p->ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  if (rotates_in_kernel(p) && getenv("ISHI_NO_FUSED_ROTATION") == nullptr)
+    return projection_matmul(p, x, rows, y, ldy, flags, true, static_cast<cudaStream_t>(stream));
   ishi_status s = ishi_projection_rotate(p, x, rows, p->xr, stream);
   if (s != ISHI_OK) return s;
-  return projection_matmul(p, p->xr, rows, y, ldy, flags, static_cast<cudaStream_t>(stream));
+  return projection_matmul(p, p->xr, rows, y, ldy, flags, false, static_cast<cudaStream_t>(stream));
 }
 
 ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, int rows, void *y_host, void *stream) {

@@ -52,6 +52,9 @@ struct FragArgs {
   int umax;             // most units in a column range
   int group_size, scale_dtype;
   int *err;             // raised when a bounded wait gives up
+  // Block Hadamard rotation of x while it is staged (0: none): xr = WHT_block(x * signs) / sqrt(block)
+  int rot_block;           // a power of two, 8 ... 256
+  const float *rot_signs;  // [K] or null
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
@@ -127,6 +130,51 @@ __device__ __forceinline__ void frag_write(const FragArgs &a, int p, int idx, fl
     if (a.out_transposed) a.y[n * a.ldy + m] = h;
     else a.y[(long long)m * a.ldy + n] = h;
   }
+}
+
+// Eight consecutive activations of one row (this lane's k = 8 * lane ... 8 * lane + 7 of a
+// 256-wide unit) through the block Hadamard rotation, all 32 lanes together. fp32 inside, radix-2
+// stages h = 1, 2, 4 in the lane and h = 8 ... block / 2 across lanes, in that order and with the
+// same roundings as hadamard_rotate_kernel, so the result is bit-identical to rotating first.
+__device__ __forceinline__ uint4 frag_rotate8(uint4 v, int block, const float *signs, int lane) {
+  float f[8];
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+  if (signs) {
+    const float4 s0 = __ldg(reinterpret_cast<const float4 *>(signs)), s1 = __ldg(reinterpret_cast<const float4 *>(signs) + 1);
+    const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(f[i], s[i]);
+  }
+#pragma unroll
+  for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (!(j & h)) {
+        const float lo = f[j], hi = f[j + h];
+        f[j] = __fadd_rn(lo, hi);
+        f[j + h] = __fsub_rn(lo, hi);
+      }
+  for (int d = 1; d < block / 8; d <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float o = __shfl_xor_sync(0xffffffffu, f[j], d);
+      f[j] = (lane & d) ? __fsub_rn(o, f[j]) : __fadd_rn(f[j], o);
+    }
+  }
+  const float scale = 1.0f / sqrtf((float)block);
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 h2 = __halves2half2(__float2half_rn(__fmul_rn(f[2 * i], scale)), __float2half_rn(__fmul_rn(f[2 * i + 1], scale)));
+    r[i] = *reinterpret_cast<const uint32_t *>(&h2);
+  }
+  return make_uint4(r[0], r[1], r[2], r[3]);
 }
 
 // sum of n <= kFragMaxWarps floats at addr, addr + stride, ...: all loads are issued before the
