@@ -124,3 +124,42 @@ def test_rotation_matches_golden(golden_dir):
         want = oracle.hadamard_rotate(x, block)
         got = hadamardRotate(dev(x), block, None)
         assert np.array_equal(got.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("bits,gs", [(4, 32), (4, 64), (4, 128), (2, 64), (2, 128)])
+def test_single_row_on_cuda_cores(bits, gs):
+    """One activation row through the CUDA-core route (fp32 FMA, warp-shuffle reduction) gives the
+    product of the tensor-core route within the same tolerance."""
+    from ishizuki_b200 import _lib
+
+    rng = np.random.default_rng(bits * 100 + gs)
+    n, k = 400, 1536  # a ragged last panel
+    w, s, b, sd, bd, bf16 = make_pack(rng, n, k, bits, gs, "bf16")
+    x = synth.activations(rng, 1, k)
+    got = VerifyMatmul.applyAny(dev(x), dev(w), sd, bd, gs, bits, route=_lib.ROUTE_GEMV)
+    assert got is not None
+    want32, _ = oracle.affine_matmul(w, s, b, bits, gs, x, bf16=bf16)
+    assert rel_err(got.cpu().numpy(), want32) < TOL
+
+
+@pytest.mark.parametrize("block", [32, 64, 128, 256, 512])
+@pytest.mark.parametrize("signed", [False, True])
+def test_rotation_inside_the_product_kernel(block, signed):
+    """apply(x) on a rotated projection equals applyRotated(rotate(x)) bit for bit, whether the
+    rotation runs inside the product kernel (blocks up to 256) or as its own kernel (512), with and
+    without a sign vector; and it matches the oracle's product on the oracle's rotation."""
+    rng = np.random.default_rng(block + int(signed))
+    n, k = 272, 2048
+    w, s, b = synth.affine_pack(rng, n, k, 4, 64, np.float16)
+    signs = np.where(rng.random(k) < 0.5, -1.0, 1.0).astype(np.float32) if signed else None
+    lin = PackedLinear(dev(w), dev(s), dev(b), None if signs is None else dev(signs), block, groupSize=64, bits=4)
+    for rows in (1, 3, 8, 11):
+        x = synth.activations(rng, rows, k)
+        y = lin(dev(x))
+        xr_dev = lin.rotate(dev(x))
+        assert torch.equal(lin.applyRotated(xr_dev), y)
+        xr = oracle.hadamard_rotate(x, block, signs) if signs is not None else oracle.hadamard_rotate(x, block)
+        assert np.array_equal(xr_dev.cpu().numpy().view(np.uint16), xr.view(np.uint16))
+        want32, _ = oracle.affine_matmul(w, s, b, 4, 64, xr)
+        assert rel_err(y.cpu().numpy(), want32) < TOL
+    lin.ctx.poll()
