@@ -168,6 +168,74 @@ def run_reference(args) -> dict:
 
 
 # --------------------------------------------------------------------------------------------------
+# every format on the gate shape (a side table beside the headline, one GPU only)
+
+
+def format_table(peak: float) -> dict:
+    """us per projection and weight GB/s of each weight format on the gate / up shape
+    (N = 17408, K = 5120) at M = 1 and M = 8: four projections with their own weights per format,
+    replayed as one CUDA graph, timed with CUDA events."""
+    import torch
+
+    from ishizuki_b200 import synth
+    from ishizuki_b200.interface import GGMLType, GGUFBlocks, PackedLinear
+
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    n, k, copies = 17408, 5120, 4
+    rng = np.random.default_rng(99)
+
+    def make(fmt):
+        if fmt == "q4_k":
+            return PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
+        if fmt == "q6_k":
+            return PackedLinear(ggml=GGUFBlocks(dev(synth.q6k_blocks(rng, n, k)), GGMLType.q6K, (n, k)))
+        if fmt == "iq2_xs":
+            return PackedLinear(ggml=GGUFBlocks(dev(synth.iq2xs_blocks(rng, n, k)), GGMLType.iq2Xs, (n, k)))
+        if fmt == "affine4_g64":
+            w, s, b = synth.affine_pack(rng, n, k, 4, 64, np.float16)
+            return PackedLinear(dev(w), dev(s), dev(b), None, 0, groupSize=64, bits=4)
+        w, sb, bb = synth.ternary_pack(rng, n, k, 128)  # "ternary2_g128_h128": rotation inside the kernel
+        return PackedLinear(dev(w), dev(sb).view(torch.bfloat16), dev(bb).view(torch.bfloat16), None, 128,
+                            groupSize=128, bits=2)
+
+    table = {}
+    stream = torch.cuda.Stream()
+    for fmt in ("q4_k", "affine4_g64", "ternary2_g128_h128", "iq2_xs", "q6_k"):
+        lins = [make(fmt) for _ in range(copies)]
+        row = {"weight_mb": lins[0].weightBytes / 1e6}
+        for m in (1, 8):
+            x = dev(synth.activations(rng, m, k))
+            outs = [torch.empty((m, n), dtype=torch.float16, device="cuda") for _ in lins]
+            with torch.cuda.stream(stream):
+                for lin, o in zip(lins, outs):
+                    lin(x, out=o)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for lin, o in zip(lins, outs):
+                        lin(x, out=o)
+                for _ in range(3):
+                    g.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                reps = 20
+                e0.record(stream)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(stream)
+                torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+            gbs = lins[0].weightBytes / us / 1e3
+            row["m%d" % m] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+        table[fmt] = row
+        del lins
+        torch.cuda.empty_cache()
+    return table
+
+
+# --------------------------------------------------------------------------------------------------
 # our arm
 
 
@@ -227,7 +295,7 @@ def run_ours(args) -> dict | None:
         # One CUDA graph per step on one GPU. With NCCL all-gathers in the step the launches stay
         # eager: capturing them together with the early-launched product kernels did not finish
         # within ten minutes when tried at two ranks, cause not established.
-        if world == 1:
+        if world == 1 or os.environ.get("ISHI_BENCH_GRAPH_MULTI") == "1":
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 one_pass()
@@ -311,6 +379,8 @@ def run_ours(args) -> dict | None:
     }
     if e2e is not None:
         out["e2e"] = e2e
+    if world == 1 and os.environ.get("ISHI_BENCH_NO_FORMATS") != "1":
+        out["formats"] = format_table(peak)
     if world == 1:
         layer = cpu_sample()
         cpu_pass(layer)
