@@ -256,6 +256,12 @@ def run_ours(args) -> dict | None:
 
     layers = args.layers
     rng = np.random.default_rng(1234)
+    use_nccl = os.environ.get("ISHI_BENCH_NCCL") == "1"  # N > 1: all-gather per projection instead of the exchange
+    exchange = None
+    if world > 1 and not use_nccl:
+        from ishizuki_b200.sharding import OutputExchange
+
+        exchange = OutputExchange(sum(((n * 16 + 255) & ~255) for _, n, _ in SHAPES) * layers + 4096)
     projections = []  # (lin, x, y_local, y_full, n_full, k)
     total_weight = 0
     total_alg = 0
@@ -268,34 +274,44 @@ def run_ours(args) -> dict | None:
             lin = PackedLinear(ggml=GGUFBlocks(dev, GGMLType.q4K, (blocks_full_rows, k)))
             del dev  # the projection keeps its own tiled copy
             x = torch.from_numpy(synth.activations(rng, ROWS, k)).cuda()
-            if world > 1:
+            if exchange is not None:
+                y_local, y_full = exchange.reserve(n)  # (byte offset, [n, 8] view of this rank's copy)
+            elif world > 1:
                 y_local = torch.empty((blocks_full_rows, ROWS), dtype=torch.float16, device="cuda")
                 y_full = torch.empty((n, ROWS), dtype=torch.float16, device="cuda")
             else:
                 y_local = torch.empty((ROWS, n), dtype=torch.float16, device="cuda")
                 y_full = y_local
-            projections.append((lin, x, y_local, y_full, n, k))
+            projections.append((lin, x, y_local, y_full, n, k, n_lo))
             total_weight += weight_bytes(n, k)
             total_alg += algorithmic_bytes(n, k, ROWS)
     torch.cuda.empty_cache()
 
     def one_pass():
-        for lin, x, y_local, y_full, _, _ in projections:
-            if world > 1:
+        for lin, x, y_local, y_full, _, _, n_lo in projections:
+            if exchange is not None:
+                # every kernel stores its rows into all ranks' copies and waits for the other
+                # ranks' previous projection first, as a layer stack's data flow would make it
+                exchange.apply(lin, x, y_local, n_lo, wait_previous=True)
+            elif world > 1:
                 lin(x, transposed=True, out=y_local)
                 dist.all_gather_into_tensor(y_full, y_local)
             else:
                 lin(x, out=y_local)
+        if exchange is not None:
+            exchange.wait()
 
     stream = torch.cuda.Stream()
     graph = None
     with torch.cuda.stream(stream):
         one_pass()
         torch.cuda.synchronize()
-        # One CUDA graph per step on one GPU. With NCCL all-gathers in the step the launches stay
-        # eager: capturing them together with the early-launched product kernels did not finish
-        # within ten minutes when tried at two ranks, cause not established.
-        if world == 1 or os.environ.get("ISHI_BENCH_GRAPH_MULTI") == "1":
+        # One CUDA graph per step. With NCCL all-gathers in the step the launches stay eager:
+        # capturing them in the graph did not finish when tried at two ranks (with and without
+        # early launch of the product kernels), cause not established.
+        if world == 1 or exchange is not None:
+            if world > 1:
+                dist.barrier()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 one_pass()
@@ -333,7 +349,7 @@ def run_ours(args) -> dict | None:
         e2e = None
         if world == 1:
             host = [(lin, np.ascontiguousarray(x.cpu().numpy()), np.empty((ROWS, n), dtype=np.float16))
-                    for lin, x, _, _, n, _ in projections]
+                    for lin, x, _, _, n, _, _ in projections]
             for lin, xh, yh in host[: len(SHAPES)]:
                 lin.apply_host(xh, yh)
             e2e_steps = max(1, min(args.steps, 5))
@@ -366,7 +382,9 @@ def run_ours(args) -> dict | None:
         "config": {
             "workload": "GGUF Q4_K MLP projections of a 27B model (K=5120/N=17408, K=17408/N=5120), M=8",
             "layers": layers, "rows": ROWS, "l2": "every projection has its own weights: %.2f GB per step" %
-            (total_weight / 1e9), "parallelism": "N-sharded x%d + all-gather" % world if world > 1 else "single GPU",
+            (total_weight / 1e9),
+            "parallelism": ("N-sharded x%d, outputs exchanged by the product kernels over NVLink" % world if exchange is not None
+                            else "N-sharded x%d + NCCL all-gather" % world) if world > 1 else "single GPU",
             "launch": "CUDA graph" if graph is not None else "eager",
         },
         "us_per_layer": ms_per_step * 1e3 / layers,

@@ -186,6 +186,42 @@ ishi_status ishi_q4k_matmul_few_static(const void *x_dev, int rows, const void *
                                        int64_t blocks_bytes, int64_t n, int64_t k, void *y_dev,
                                        void *stream);
 
+/* ---- N-sharded projections: output exchange over NVLink ---------------------------------------
+ *
+ * The reference runs on one GPU; these have no counterpart in it. Each rank (one process per GPU)
+ * holds the rows [r*N/G, (r+1)*N/G) of every projection (desc.n = rows of the shard). Instead of
+ * a collective after the product, the product kernel stores its rows into every rank's copy of
+ * the output through peer mappings, and the ranks tell each other with arrival words: no extra
+ * kernel, nothing on the host, the whole step can be one CUDA graph.
+ *
+ * An exchange owns, on every rank, one buffer of out_bytes for outputs and a few arrival words.
+ * Outputs are fp16 arrays [rows of all shards][8]: row n holds the (up to 8) drafted rows'
+ * values of output n, the transposed form of ishi_projection_apply. All ranks must issue the same
+ * sequence of ishi_exchange_apply calls. Waits on the device are bounded (about a second) and
+ * raise the context's error word (ishi_ctx_poll) instead of hanging. */
+typedef struct ishi_exchange ishi_exchange;
+enum { ISHI_EXCHANGE_HANDLE_BYTES = 128 };
+/* Allocates this rank's buffer (cudaMalloc) and arrival words. */
+ishi_status ishi_exchange_create(ishi_ctx *ctx, int rank, int world, int64_t out_bytes,
+                                 ishi_exchange **out);
+/* Writes ISHI_EXCHANGE_HANDLE_BYTES bytes the other ranks need to map this rank's buffers (CUDA
+ * IPC handles); the host passes them around by any means it has. */
+ishi_status ishi_exchange_export(ishi_exchange *ex, void *handle_out);
+/* handles: world x ISHI_EXCHANGE_HANDLE_BYTES, rank by rank (this rank's own entry is ignored). */
+ishi_status ishi_exchange_connect(ishi_exchange *ex, const void *handles);
+/* This rank's output buffer (device pointer). */
+void *ishi_exchange_buffer(ishi_exchange *ex);
+/* x [rows, k] (rows 1...8) against this rank's shard; the rows land at
+ * buffer + out_offset_bytes, rows [row_offset, row_offset + n) of the [.][8] array, on every rank.
+ * wait_previous != 0: the kernel first waits until every rank's previous ishi_exchange_apply has
+ * landed here (use it when x was produced from exchanged outputs). */
+ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const void *x_dev, int rows,
+                                int64_t out_offset_bytes, int64_t row_offset, int wait_previous,
+                                void *stream);
+/* Enqueues a wait for every rank's latest ishi_exchange_apply to have landed in this rank's buffer. */
+ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream);
+void ishi_exchange_destroy(ishi_exchange *ex);
+
 #ifdef __cplusplus
 }
 #endif

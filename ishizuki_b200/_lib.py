@@ -14,6 +14,7 @@ KIND_AFFINE, KIND_GGML = 0, 1
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 ROUTE_AUTO, ROUTE_GEMV, ROUTE_MMA = 0, 1, 2
 OUT_TRANSPOSED = 1
+EXCHANGE_HANDLE_BYTES = 128
 
 
 class WeightDesc(ctypes.Structure):
@@ -54,6 +55,13 @@ SIGNATURES = {
     "ishi_ggml_block_size": (c_int, [c_int]),
     "ishi_ggml_type_size": (c_int, [c_int]),
     "ishi_q4k_matmul_few_static": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ishi_exchange_create": (c_int, [c_void_p, c_int, c_int, c_int64, POINTER(c_void_p)]),
+    "ishi_exchange_export": (c_int, [c_void_p, c_void_p]),
+    "ishi_exchange_connect": (c_int, [c_void_p, c_void_p]),
+    "ishi_exchange_buffer": (c_void_p, [c_void_p]),
+    "ishi_exchange_apply": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p]),
+    "ishi_exchange_wait": (c_int, [c_void_p, c_void_p]),
+    "ishi_exchange_destroy": (None, [c_void_p]),
 }
 
 _lib = None

@@ -560,9 +560,20 @@ ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args,
   return ISHI_OK;
 }
 
+// where a sharded product stores its rows (see ishi_exchange_apply)
+struct PeerOut {
+  int world, rank;
+  __half *y[kFragMaxPeers];
+  unsigned *flags[kFragMaxPeers];
+  unsigned *local_flags, *done, *launch_no;
+  int wait_previous;
+  long long row_offset;
+};
+
 // rows 1...16 through the warp-level kernel; gemv picks the CUDA-core variant for a single row
 ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, const ishi_weight_desc &d, const void *x,
-                     int rows, void *y, long long ldy, int flags, bool gemv, bool early, bool rotate, cudaStream_t st) {
+                     int rows, void *y, long long ldy, int flags, bool gemv, bool early, bool rotate, cudaStream_t st,
+                     const PeerOut *peers = nullptr) {
   for (int r0 = 0; r0 < rows; r0 += 8) {
     FragArgs a;
     memset(&a, 0, sizeof(a));
@@ -591,6 +602,19 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.err = ctx->err_dev;
     a.rot_block = rotate ? d.hadamard_block : 0;
     a.rot_signs = rotate ? static_cast<const float *>(d.signs_dev) : nullptr;
+    if (peers) {
+      a.world = peers->world;
+      a.rank = peers->rank;
+      for (int q = 0; q < peers->world; ++q) {
+        a.peer_y[q] = peers->y[q];
+        a.peer_flags[q] = peers->flags[q];
+      }
+      a.local_flags = peers->local_flags;
+      a.done = peers->done;
+      a.launch_no = peers->launch_no;
+      a.wait_previous = peers->wait_previous;
+      a.row_offset = peers->row_offset;
+    }
     const bool single = gemv && rows == 1;
     ishi_status s = with_frag_format(pl.fmt_id, [&](auto tag) {
       typedef typename decltype(tag)::type Fmt;
@@ -1007,6 +1031,142 @@ ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, i
 }
 
 }  // extern "C"
+
+// ---- output exchange between the GPUs of an N-sharded projection ---------------------------------
+
+struct ishi_exchange {
+  ishi_ctx *ctx = nullptr;
+  int rank = 0, world = 1;
+  uint8_t *buf = nullptr;
+  size_t bytes = 0;
+  unsigned *words = nullptr;  // [0, world): arrival words; [16]: CTAs done; [17]: number of the last launch
+  uint8_t *peer_buf[kFragMaxPeers] = {nullptr};
+  unsigned *peer_words[kFragMaxPeers] = {nullptr};
+  bool connected = false;
+};
+
+struct ExchangeHandle {
+  cudaIpcMemHandle_t buf, words;
+};
+static_assert(sizeof(ExchangeHandle) <= ISHI_EXCHANGE_HANDLE_BYTES, "two IPC handles fit the exported blob");
+
+ishi_status ishi_exchange_create(ishi_ctx *ctx, int rank, int world, int64_t out_bytes, ishi_exchange **out) {
+  if (!ctx || !out) return ISHI_E_INVALID;
+  *out = nullptr;
+  if (world < 1 || world > kFragMaxPeers || rank < 0 || rank >= world || out_bytes < 16)
+    return fail(ctx, ISHI_E_INVALID, "exchange of rank %d of %d, %lld bytes", rank, world, (long long)out_bytes);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ishi_exchange *ex = new (std::nothrow) ishi_exchange();
+  if (!ex) return fail(ctx, ISHI_E_NOMEM, "host allocation failed");
+  ex->ctx = ctx;
+  ex->rank = rank;
+  ex->world = world;
+  ex->bytes = (size_t)out_bytes;
+  cudaError_t e = cudaMalloc(&ex->buf, ex->bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&ex->words, 256);
+  if (e == cudaSuccess) e = cudaMemset(ex->words, 0, 256);
+  if (e == cudaSuccess) e = cudaMemset(ex->buf, 0, ex->bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (ex->buf) cudaFree(ex->buf);
+    if (ex->words) cudaFree(ex->words);
+    delete ex;
+    return fail(ctx, ISHI_E_NOMEM, "exchange buffers: %s", cudaGetErrorString(e));
+  }
+  ex->peer_buf[rank] = ex->buf;
+  ex->peer_words[rank] = ex->words;
+  ex->connected = world == 1;
+  *out = ex;
+  return ISHI_OK;
+}
+
+ishi_status ishi_exchange_export(ishi_exchange *ex, void *handle_out) {
+  if (!ex || !handle_out) return ISHI_E_INVALID;
+  ishi_ctx *ctx = ex->ctx;
+  ExchangeHandle h;
+  memset(&h, 0, sizeof(h));
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ISHI_CUDA(ctx, cudaIpcGetMemHandle(&h.buf, ex->buf));
+  ISHI_CUDA(ctx, cudaIpcGetMemHandle(&h.words, ex->words));
+  memset(handle_out, 0, ISHI_EXCHANGE_HANDLE_BYTES);
+  memcpy(handle_out, &h, sizeof(h));
+  return ISHI_OK;
+}
+
+ishi_status ishi_exchange_connect(ishi_exchange *ex, const void *handles) {
+  if (!ex || !handles) return ISHI_E_INVALID;
+  ishi_ctx *ctx = ex->ctx;
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  for (int q = 0; q < ex->world; ++q) {
+    if (q == ex->rank || ex->peer_buf[q]) continue;
+    ExchangeHandle h;
+    memcpy(&h, static_cast<const uint8_t *>(handles) + (size_t)q * ISHI_EXCHANGE_HANDLE_BYTES, sizeof(h));
+    void *b = nullptr, *w = nullptr;
+    ISHI_CUDA(ctx, cudaIpcOpenMemHandle(&b, h.buf, cudaIpcMemLazyEnablePeerAccess));
+    ISHI_CUDA(ctx, cudaIpcOpenMemHandle(&w, h.words, cudaIpcMemLazyEnablePeerAccess));
+    ex->peer_buf[q] = static_cast<uint8_t *>(b);
+    ex->peer_words[q] = static_cast<unsigned *>(w);
+  }
+  ex->connected = true;
+  return ISHI_OK;
+}
+
+void *ishi_exchange_buffer(ishi_exchange *ex) { return ex ? ex->buf : nullptr; }
+
+ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const void *x, int rows, int64_t out_offset_bytes,
+                                int64_t row_offset, int wait_previous, void *stream) {
+  if (!ex || !p) return ISHI_E_INVALID;
+  ishi_ctx *ctx = ex->ctx;
+  if (p->ctx != ctx) return fail(ctx, ISHI_E_INVALID, "projection and exchange belong to different contexts");
+  if (!ex->connected) return fail(ctx, ISHI_E_INVALID, "exchange not connected");
+  if (!p->frag.ok) return fail(ctx, ISHI_E_UNSUPPORTED, "this weight format has no kernel with an output exchange");
+  if (!x) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (rows < 1 || rows > 8) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...8", rows);
+  if (out_offset_bytes < 0 || (out_offset_bytes & 15) || row_offset < 0 ||
+      (size_t)out_offset_bytes + (size_t)(row_offset + p->d.n) * 16 > ex->bytes)
+    return fail(ctx, ISHI_E_SHAPE, "rows %lld...%lld at offset %lld do not fit the exchange buffer", (long long)row_offset,
+                (long long)(row_offset + p->d.n), (long long)out_offset_bytes);
+  const int b = p->d.hadamard_block;
+  if (b != 0 && !rotates_in_kernel(p)) return fail(ctx, ISHI_E_UNSUPPORTED, "rotation block %d needs its own kernel", b);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  PeerOut po;
+  memset(&po, 0, sizeof(po));
+  po.world = ex->world;
+  po.rank = ex->rank;
+  for (int q = 0; q < ex->world; ++q) {
+    po.y[q] = reinterpret_cast<__half *>(ex->peer_buf[q] + out_offset_bytes);
+    po.flags[q] = ex->peer_words[q];
+  }
+  po.local_flags = ex->words;
+  po.done = ex->words + 16;
+  po.launch_no = ex->words + 17;
+  po.wait_previous = wait_previous ? 1 : 0;
+  po.row_offset = row_offset;
+  return run_frag(ctx, p->frag, p->ws, p->d, x, rows, ex->buf + out_offset_bytes, 8, ISHI_OUT_TRANSPOSED, false,
+                  getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, b != 0, static_cast<cudaStream_t>(stream), &po);
+}
+
+ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream) {
+  if (!ex) return ISHI_E_INVALID;
+  ishi_ctx *ctx = ex->ctx;
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ex->words, ex->world, ex->words + 17, ctx->err_dev);
+  ISHI_CUDA(ctx, cudaGetLastError());
+  return ISHI_OK;
+}
+
+void ishi_exchange_destroy(ishi_exchange *ex) {
+  if (!ex) return;
+  cudaSetDevice(ex->ctx->device);
+  for (int q = 0; q < ex->world; ++q) {
+    if (q == ex->rank) continue;
+    if (ex->peer_buf[q]) cudaIpcCloseMemHandle(ex->peer_buf[q]);
+    if (ex->peer_words[q]) cudaIpcCloseMemHandle(ex->peer_words[q]);
+  }
+  if (ex->buf) cudaFree(ex->buf);
+  if (ex->words) cudaFree(ex->words);
+  delete ex;
+}
 
 // ---- the entry point for callers that cannot allocate ---------------------------------------------
 //

@@ -36,6 +36,7 @@ constexpr int kFragMaxWarps = 20;
 constexpr int kFragRing = 3;      // tiles per warp-private ring: two in flight while one is decoded
 constexpr int kFragGroup = 4;     // most panels of one warp between two CTA barriers
 constexpr int kFragMaxSplit = 8;  // portable cluster size
+constexpr int kFragMaxPeers = 8;  // GPUs of one NVSwitch box
 
 struct FragArgs {
   const uint8_t *tiles;  // [P][units][tile bytes]
@@ -55,6 +56,21 @@ struct FragArgs {
   // Block Hadamard rotation of x while it is staged (0: none): xr = WHT_block(x * signs) / sqrt(block)
   int rot_block;           // a power of two, 8 ... 256
   const float *rot_signs;  // [K] or null
+  // Output exchange between the GPUs of an N-sharded projection (world = 0: none). Every rank holds
+  // the whole output as [rows of all shards][8] fp16 at the same place of its exchange buffer; this
+  // launch computes rows row_offset ... row_offset + N - 1 and stores them into every rank's copy
+  // over NVLink. When all CTAs have stored, the rank writes seq into its arrival word on every rank.
+  int world, rank;
+  __half *peer_y[kFragMaxPeers];          // the output array in every rank's buffer ([rank]: the local one)
+  unsigned *peer_flags[kFragMaxPeers];    // every rank's arrival words; this rank writes word [rank] of each
+  unsigned *local_flags;                  // this rank's arrival words, one per rank
+  unsigned *done;                         // CTAs of this launch that have stored their rows
+  // The launches of an exchange are numbered on the device (so that a captured graph can be
+  // replayed): *launch_no is the number of the last launch that completed on this rank; all ranks
+  // issue the same sequence, so the numbers agree across ranks.
+  unsigned *launch_no;
+  int wait_previous;                      // first wait until every rank's previous launch has arrived here
+  long long row_offset;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
@@ -119,9 +135,35 @@ __host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, i
          (size_t)W * kFragRing * frag_ring_stride(tile_bytes);
 }
 
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // element idx of panel p in accumulator-fragment order: lane idx / 4 (g = lane / 4, t = lane % 4),
-// register e = idx % 4 -> weight row g + 8 * (e / 2), activation row 2t + e % 2
+// register e = idx % 4 -> weight row g + 8 * (e / 2), activation row 2t + e % 2.
+// With an output exchange the 32 lanes of a warp hold 32 consecutive elements (two weight rows
+// g, two rows g + 8, eight activation rows each): they gather each row's eight values in one lane,
+// which stores the 16 bytes into every rank's copy.
 __device__ __forceinline__ void frag_write(const FragArgs &a, int p, int idx, float v) {
+  if (a.world > 0) {
+    const uint32_t mine = __half_as_ushort(__float2half_rn(v));
+    const uint32_t pair = mine | (__shfl_down_sync(0xffffffffu, mine, 1) << 16);  // activation rows 2t, 2t + 1 (even idx)
+    const uint32_t w1 = __shfl_down_sync(0xffffffffu, pair, 4), w2 = __shfl_down_sync(0xffffffffu, pair, 8);
+    const uint32_t w3 = __shfl_down_sync(0xffffffffu, pair, 12);
+    if ((idx & 13) == 0) {  // t = 0 and an even register: weight row g + 8 * ((idx >> 1) & 1)
+      const long long n = (long long)p * kFragRows + (idx >> 4) + ((idx & 2) ? 8 : 0);
+      if (n < a.N) {
+        const uint4 row = make_uint4(pair, w1, w2, w3);
+        for (int q = 0; q < a.world; ++q) *reinterpret_cast<uint4 *>(a.peer_y[q] + (a.row_offset + n) * 8) = row;
+      }
+    }
+    return;
+  }
   const int ln = idx >> 2, e = idx & 3;
   const long long n = (long long)p * kFragRows + (ln >> 2) + ((e & 2) ? 8 : 0);
   const int m = 2 * (ln & 3) + (e & 1);
@@ -269,6 +311,22 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   // one and y may still be read by it: wait for the earlier kernels (returns at once unless this
   // kernel was launched early).
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  unsigned previous_launch = 0;
+  if (a.world > 0) {
+    previous_launch = *reinterpret_cast<volatile unsigned *>(a.launch_no);
+    if (a.wait_previous && previous_launch != 0) {
+      // ... and for the other GPUs: x may be rows they stored into this rank's exchange buffer
+      if ((int)threadIdx.x < a.world) {
+        bool ok = false;
+        for (uint32_t i = 0; i < kWaitSpins && !ok; ++i) {
+          ok = (int)(ld_acquire_sys(a.local_flags + threadIdx.x) - previous_launch) >= 0;
+          if (!ok) __nanosleep(64);
+        }
+        if (!ok) *a.err = 2;  // give up: the result is wrong, the error word tells the host
+      }
+      __syncthreads();
+    }
+  }
 
   // activations of the column range into fragment order (all warps), while the first tiles fly
   Fmt::stage_x(a, xfrag, ub0, uc);
@@ -378,6 +436,33 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
     cluster_wait_relaxed();
   }
   cp_async_wait<0>();
+  if (a.world > 0) {
+    // this CTA's rows are on their way to every rank; the last CTA of the launch announces them
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned before = atomicAdd(a.done, 1u);
+      if (before == gridDim.x - 1) {
+        *reinterpret_cast<volatile unsigned *>(a.done) = 0u;  // for the next launch on this stream
+        *reinterpret_cast<volatile unsigned *>(a.launch_no) = previous_launch + 1u;
+        __threadfence_system();
+        for (int q = 0; q < a.world; ++q) st_release_sys(a.peer_flags[q] + a.rank, previous_launch + 1u);
+      }
+    }
+  }
+}
+
+// waits (bounded) until every rank's arrival word has reached this rank's latest launch
+__global__ void peer_wait_kernel(const unsigned *local_flags, int world, const unsigned *launch_no, int *err) {
+  if ((int)threadIdx.x < world) {
+    const unsigned seq = *reinterpret_cast<const volatile unsigned *>(launch_no);
+    bool ok = false;
+    for (uint32_t i = 0; i < kWaitSpins && !ok; ++i) {
+      ok = (int)(ld_acquire_sys(local_flags + threadIdx.x) - seq) >= 0;
+      if (!ok) __nanosleep(64);
+    }
+    if (!ok) *err = 2;
+  }
 }
 
 // One-time re-tiling into fragment order: Fmt::tile_halfword says which 2 bytes of the source

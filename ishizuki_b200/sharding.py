@@ -72,3 +72,88 @@ class ShardedLinear:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         y_local_t = self.local(x, transposed=True)
         return gather_rows(y_local_t, self.n, self.group).t()
+
+
+class _DeviceView:
+    """A raw device range as something torch.as_tensor accepts (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class OutputExchange:
+    """Outputs of N-sharded projections exchanged by the product kernels themselves over NVLink
+    (ishi_exchange_* in the C ABI) instead of one all-gather per projection: every rank's kernel
+    stores its rows into every rank's copy of the output and the ranks signal each other with
+    arrival words, so a whole step has no collective and can be captured in one CUDA graph.
+
+    The buffer holds fp16 arrays [rows of all shards][8] at offsets handed out by reserve();
+    all ranks must reserve and apply in the same order. The handles are exchanged once over the
+    (host) process group."""
+
+    def __init__(self, nbytes: int, group=None, device: int | None = None):
+        import ctypes
+
+        from . import _lib
+        from .interface import Context, IshizukiError
+
+        self._err = IshizukiError
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.ctx = Context.get(torch.cuda.current_device() if device is None else device)
+        self.lib = self.ctx.lib
+        self.nbytes = int(nbytes)
+        self.used = 0
+        handle = ctypes.c_void_p()
+        self._check(self.lib.ishi_exchange_create(self.ctx.handle, self.rank, self.world, self.nbytes, ctypes.byref(handle)))
+        self.handle = handle
+        if self.world > 1:
+            blob = ctypes.create_string_buffer(_lib.EXCHANGE_HANDLE_BYTES)
+            self._check(self.lib.ishi_exchange_export(self.handle, blob))
+            blobs = [None] * self.world
+            dist.all_gather_object(blobs, bytes(blob.raw), group=group)
+            joined = ctypes.create_string_buffer(b"".join(blobs), _lib.EXCHANGE_HANDLE_BYTES * self.world)
+            self._check(self.lib.ishi_exchange_connect(self.handle, joined))
+            dist.barrier(group=group)
+        base = self.lib.ishi_exchange_buffer(self.handle)
+        self.buffer = torch.as_tensor(_DeviceView(base, self.nbytes), device=torch.device("cuda", self.ctx.device))
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise self._err(rc, self.ctx.last_error())
+
+    def reserve(self, n_total: int) -> tuple[int, torch.Tensor]:
+        """Room for one output [n_total, 8] fp16: its byte offset and a view of the local copy."""
+        off = self.used
+        size = n_total * 16
+        if off + size > self.nbytes:
+            raise ValueError(f"exchange buffer of {self.nbytes} bytes is full")
+        self.used = off + ((size + 255) & ~255)
+        return off, self.buffer[off: off + size].view(torch.float16).view(n_total, 8)
+
+    def apply(self, local, x: torch.Tensor, offset: int, row_offset: int, wait_previous: bool = True) -> None:
+        """local: interface.PackedLinear over this rank's rows; x [rows <= 8, K] fp16 on this GPU."""
+        import ctypes
+
+        rows = x.shape[0]
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._check(self.lib.ishi_exchange_apply(self.handle, local.handle, ctypes.c_void_p(x.data_ptr()), rows, offset,
+                                                 row_offset, 1 if wait_previous else 0, stream))
+
+    def wait(self) -> None:
+        """Enqueues, on the current stream, a wait for every rank's latest apply to have landed here."""
+        import ctypes
+
+        self._check(self.lib.ishi_exchange_wait(self.handle, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.ishi_exchange_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

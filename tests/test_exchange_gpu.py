@@ -1,0 +1,83 @@
+"""The NVLink output exchange of N-sharded projections (ishi_exchange_* in the C ABI).
+
+On one GPU the exchange degenerates to "the kernel writes its rows into the local [N, 8] array and
+raises its own arrival word": that path is checked against the plain projection. With two or more
+GPUs a two-process run (one rank per GPU) checks that every rank ends up with the whole output.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from ishizuki_b200 import synth
+from ishizuki_b200.interface import GGMLType, GGUFBlocks, PackedLinear
+from ishizuki_b200.sharding import OutputExchange
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("rows", [1, 5, 8])
+def test_single_rank_exchange_matches_projection(rows):
+    rng = np.random.default_rng(rows)
+    n, k = 1000, 2048  # a ragged last panel
+    lin = PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
+    ex = OutputExchange(4 << 20)
+    off_a, view_a = ex.reserve(n)
+    off_b, view_b = ex.reserve(n)
+    x = dev(synth.activations(rng, rows, k))
+    want = lin(x, transposed=True)
+    for _ in range(3):  # the launch numbers advance; every call waits for the one before
+        ex.apply(lin, x, off_a, 0)
+        ex.apply(lin, x, off_b, 0)
+    ex.wait()
+    torch.cuda.synchronize()
+    lin.ctx.poll()
+    assert torch.equal(view_a[:, :rows], want)
+    assert torch.equal(view_b[:, :rows], want)
+    assert not view_a[:, rows:].any()
+    ex.close()
+
+
+def test_single_rank_exchange_in_a_replayed_graph():
+    rng = np.random.default_rng(7)
+    n, k = 768, 1024
+    w, s, b = synth.affine_pack(rng, n, k, 4, 64, np.float16)
+    lin = PackedLinear(dev(w), dev(s), dev(b), None, 0, groupSize=64, bits=4)
+    ex = OutputExchange(1 << 20)
+    off, view = ex.reserve(n)
+    x = dev(synth.activations(rng, 8, k))
+    want = lin(x, transposed=True)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ex.apply(lin, x, off, 0)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            ex.apply(lin, x, off, 0)
+            ex.apply(lin, x, off, 0)
+            ex.wait()
+        for _ in range(4):
+            view.zero_()
+            graph.replay()
+        torch.cuda.synchronize()
+    lin.ctx.poll()
+    assert torch.equal(view, want)
+    ex.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_exchange_whole_outputs():
+    script = os.path.join(os.path.dirname(__file__), "exchange_two_ranks.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", script]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
+    assert done.stdout.count("exchange ok") == 2
