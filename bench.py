@@ -3,7 +3,7 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1]): GGUF Q4_K projections with the MLP shapes of a 27B model,
+Workload: GGUF Q4_K projections with the MLP shapes of a 27B model,
 gate / up (K = 5120, N = 17408) and down (K = 17408, N = 5120), against M = 8 drafted rows
 (fp16 activations, fp32 accumulate, fp16 outputs). One step is one pass over `layers` such MLP
 blocks, every projection with its own weight buffer, so a step streams layers * 150 MB of
@@ -38,8 +38,8 @@ ROWS = 8
 METRIC = "quantized-matmul weight GB/s (% of HBM peak) at M=1/8 draft rows; µs/layer"
 
 
-# dram__bytes read + written per launch of the product kernel, from the ncu capture summarised in
-# profiles/frag_kernel_q4k_mlp_m8.md (mean of gate, up, down: 50.28, 50.28, 50.49 MB)
+# dram__bytes read + written per launch of the product kernel, from the ncu capture summarised
+# under profiles/ (mean of gate, up, down: 50.28, 50.28, 50.49 MB)
 NCU_DRAM_BYTES_PER_LAUNCH = 50.35e6
 
 
@@ -287,12 +287,19 @@ def run_ours(args) -> dict | None:
             total_alg += algorithmic_bytes(n, k, ROWS)
     torch.cuda.empty_cache()
 
+    # Which projections wait for the other ranks' previous exchange, in the order gate, up, down:
+    # gate reads the previous block's down output and down reads gate and up, so both wait; up reads
+    # what gate already waited for. ISHI_BENCH_WAITS=111 makes every projection wait, 000 none.
+    WAITS = [c == "1" for c in os.environ.get("ISHI_BENCH_WAITS", "101")]
+    waits_seen = []
+
     def one_pass():
         for lin, x, y_local, y_full, _, _, n_lo in projections:
             if exchange is not None:
                 # every kernel stores its rows into all ranks' copies and waits for the other
                 # ranks' previous projection first, as a layer stack's data flow would make it
-                exchange.apply(lin, x, y_local, n_lo, wait_previous=True)
+                exchange.apply(lin, x, y_local, n_lo, wait_previous=WAITS[len(waits_seen) % 3])
+                waits_seen.append(0)
             elif world > 1:
                 lin(x, transposed=True, out=y_local)
                 dist.all_gather_into_tensor(y_full, y_local)

@@ -437,10 +437,11 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   }
   cp_async_wait<0>();
   if (a.world > 0) {
-    // this CTA's rows are on their way to every rank; the last CTA of the launch announces them
-    __threadfence_system();
+    // this CTA's rows are on their way to every rank; the last CTA of the launch announces them.
+    // One thread fences for the CTA: the barrier orders the other threads' stores before it.
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const unsigned before = atomicAdd(a.done, 1u);
       if (before == gridDim.x - 1) {
         *reinterpret_cast<volatile unsigned *>(a.done) = 0u;  // for the next launch on this stream
