@@ -140,8 +140,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned *p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // element idx of panel p in accumulator-fragment order: lane idx / 4 (g = lane / 4, t = lane % 4),
@@ -437,8 +437,11 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   }
   cp_async_wait<0>();
   if (a.world > 0) {
-    // this CTA's rows are on their way to every rank; the last CTA of the launch announces them.
-    // One thread fences for the CTA: the barrier orders the other threads' stores before it.
+    // This CTA's rows are on their way to every rank; the last CTA of the launch announces them.
+    // One thread fences for the CTA (the barrier orders the other threads' stores before it), at
+    // system scope, so the rows have landed everywhere before the CTA counts itself done. The CTA
+    // that counts last has therefore seen every CTA's rows land and needs no further fence before
+    // it raises the arrival words (a system-scope fence costs microseconds).
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence_system();
@@ -446,8 +449,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       if (before == gridDim.x - 1) {
         *reinterpret_cast<volatile unsigned *>(a.done) = 0u;  // for the next launch on this stream
         *reinterpret_cast<volatile unsigned *>(a.launch_no) = previous_launch + 1u;
-        __threadfence_system();
-        for (int q = 0; q < a.world; ++q) st_release_sys(a.peer_flags[q] + a.rank, previous_launch + 1u);
+        for (int q = 0; q < a.world; ++q) st_relaxed_sys(a.peer_flags[q] + a.rank, previous_launch + 1u);
       }
     }
   }
