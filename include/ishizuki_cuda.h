@@ -121,6 +121,14 @@ ishi_status ishi_projection_apply_rotated(ishi_projection *p, const void *xr_dev
  * copies y out, all on the stream; returns once y_host is complete. */
 ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, int rows,
                                        void *y_host, void *stream);
+/* The same without the wait: enqueues the copy of x_host [rows, k] to the device, the product and
+ * the copy of y [rows, n] back into y_host on the stream and returns. Both host buffers must stay
+ * untouched until the stream has been synchronised; with page-locked host memory the copies
+ * overlap the host, with pageable memory the runtime stages them. Calls on one projection must
+ * be ordered on one stream (they share its device staging, allocated by the first call). Errors a
+ * kernel raises show in ishi_ctx_poll after the synchronisation. */
+ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_host, int rows,
+                                             void *y_host, void *stream);
 
 /* ---- kernel level ------------------------------------------------------------------------- */
 

@@ -83,6 +83,7 @@ struct ishi_projection {
   FragPlan frag;         // warp-level kernel
   Workspace ws;          // this projection's own scratch and tiled weight: apply never allocates
   __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
+  __half *host_x = nullptr, *host_y = nullptr;  // device staging of apply_host_async: [16][k], [16][n]
   int64_t weight_bytes = 0;
 };
 
@@ -945,6 +946,8 @@ void ishi_projection_destroy(ishi_projection *p) {
   cudaSetDevice(p->ctx->device);
   free_workspace(&p->ws);
   if (p->xr) cudaFree(p->xr);
+  if (p->host_x) cudaFree(p->host_x);
+  if (p->host_y) cudaFree(p->host_y);
   delete p;
 }
 
@@ -987,6 +990,37 @@ ishi_status ishi_projection_apply(ishi_projection *p, const void *x, int rows, v
   ishi_status s = ishi_projection_rotate(p, x, rows, p->xr, stream);
   if (s != ISHI_OK) return s;
   return projection_matmul(p, p->xr, rows, y, ldy, flags, false, static_cast<cudaStream_t>(stream));
+}
+
+ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_host, int rows, void *y_host,
+                                             void *stream) {
+  if (!p) return ISHI_E_INVALID;
+  ishi_ctx *ctx = p->ctx;
+  if (!x_host || !y_host) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!p->host_x) {
+    // the first call allocates this projection's device staging (make it outside stream capture)
+    std::lock_guard<std::mutex> g(ctx->lock);
+    if (!p->host_x) {
+      __half *hx = nullptr, *hy = nullptr;
+      ISHI_CUDA(ctx, cudaMalloc(&hx, (size_t)16 * p->d.k * sizeof(__half)));
+      cudaError_t e = cudaMalloc(&hy, (size_t)16 * p->d.n * sizeof(__half));
+      if (e != cudaSuccess) {
+        cudaFree(hx);
+        return fail(ctx, ISHI_E_NOMEM, "device staging: %s", cudaGetErrorString(e));
+      }
+      p->host_y = hy;
+      p->host_x = hx;
+    }
+  }
+  const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * p->d.n * sizeof(__half);
+  ISHI_CUDA(ctx, cudaMemcpyAsync(p->host_x, x_host, xb, cudaMemcpyHostToDevice, st));
+  ishi_status s = ishi_projection_apply(p, p->host_x, rows, p->host_y, p->d.n, 0, stream);
+  if (s != ISHI_OK) return s;
+  ISHI_CUDA(ctx, cudaMemcpyAsync(y_host, p->host_y, yb, cudaMemcpyDeviceToHost, st));
+  return ISHI_OK;
 }
 
 ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, int rows, void *y_host, void *stream) {

@@ -219,17 +219,23 @@ __device__ __forceinline__ uint4 frag_rotate8(uint4 v, int block, const float *s
   return make_uint4(r[0], r[1], r[2], r[3]);
 }
 
-// sum of n <= kFragMaxWarps floats at addr, addr + stride, ...: all loads are issued before the
-// first add, so the latency of shared memory is paid once
-__device__ __forceinline__ float lds_sum(uint32_t addr, uint32_t stride, int n) {
-  float v[kFragMaxWarps];
+// sum of n <= MAX floats at addr, addr + stride, ...: all loads are issued before the first add, so
+// the latency of shared memory is paid once
+template <int MAX>
+__device__ __forceinline__ float lds_sum_upto(uint32_t addr, uint32_t stride, int n) {
+  float v[MAX];
 #pragma unroll
-  for (int i = 0; i < kFragMaxWarps; ++i) v[i] = i < n ? lds32f(addr + (uint32_t)i * stride) : 0.f;
+  for (int i = 0; i < MAX; ++i) v[i] = i < n ? lds32f(addr + (uint32_t)i * stride) : 0.f;
 #pragma unroll
-  for (int w = 1; w < kFragMaxWarps; w *= 2)
+  for (int w = 1; w < MAX; w *= 2)
 #pragma unroll
-    for (int i = 0; i + w < kFragMaxWarps; i += 2 * w) v[i] += v[i + w];
+    for (int i = 0; i + w < MAX; i += 2 * w) v[i] += v[i + w];
   return v[0];
+}
+__device__ __forceinline__ float lds_sum(uint32_t addr, uint32_t stride, int n) {
+  if (n <= 4) return lds_sum_upto<4>(addr, stride, n);
+  if (n <= 8) return lds_sum_upto<8>(addr, stride, n);
+  return lds_sum_upto<kFragMaxWarps>(addr, stride, n);
 }
 
 // MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row.

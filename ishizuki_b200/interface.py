@@ -347,6 +347,15 @@ class PackedLinear:
         if rc != _lib.OK:
             raise IshizukiError(rc, self.ctx.last_error())
 
+    def apply_host_async(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """Host-buffer form without the wait: x_host [M, K] and y_host [M, N] are contiguous fp16 CPU
+        tensors (page-locked ones make the copies asynchronous); y_host is valid once the current
+        stream has been synchronised."""
+        rc = self.ctx.lib.ishi_projection_apply_host_async(self.handle, _ptr(x_host), x_host.shape[0], _ptr(y_host),
+                                                           _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+
 
 def hadamardRotate(x: torch.Tensor, block: int, signs: torch.Tensor | None) -> torch.Tensor:  # noqa: N802
     """xr = WHT_block(x * signs) / sqrt(block) along the last axis (forward form only)."""

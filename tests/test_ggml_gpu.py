@@ -112,3 +112,24 @@ def test_product_guards():
     assert GGMLKernels.matmulFew(ragged, blocks, GGMLType.q4K, 1) is None  # k not whole blocks
     x = torch.zeros((1, 256), dtype=torch.float16, device="cuda")
     assert GGMLKernels.matmulFew(x, blocks, GGMLType.q4K, 4) is None  # buffer too short for 4 rows
+
+
+def test_host_buffer_entry_points_agree():
+    """apply_host (waits) and apply_host_async (one synchronisation for several calls) give the
+    device path's result."""
+    rng = np.random.default_rng(5)
+    n, k = 1536, 2048
+    lin = PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
+    xs = [synth.activations(rng, m, k) for m in (1, 8, 13)]
+    want = [lin(dev(x)).cpu() for x in xs]
+    outs = [torch.empty((x.shape[0], n), dtype=torch.float16).pin_memory() for x in xs]
+    pinned = [torch.from_numpy(x).pin_memory() for x in xs]
+    for xh, yh in zip(pinned, outs):
+        lin.apply_host_async(xh, yh)
+    torch.cuda.current_stream().synchronize()
+    lin.ctx.poll()
+    for yh, w, x in zip(outs, want, xs):
+        assert torch.equal(yh, w)
+        y2 = np.empty((x.shape[0], n), dtype=np.float16)
+        lin.apply_host(x, y2)
+        assert np.array_equal(y2.view(np.uint16), w.numpy().view(np.uint16))
