@@ -258,10 +258,24 @@ def run_ours(args) -> dict | None:
     rng = np.random.default_rng(1234)
     use_nccl = os.environ.get("ISHI_BENCH_NCCL") == "1"  # N > 1: all-gather per projection instead of the exchange
     exchange = None
+    exchange_note = None
     if world > 1 and not use_nccl:
         from ishizuki_b200.sharding import OutputExchange
 
-        exchange = OutputExchange(sum(((n * 16 + 255) & ~255) for _, n, _ in SHAPES) * layers + 4096)
+        # all ranks take the same path: if one cannot map its peers, every rank falls back to NCCL
+        try:
+            exchange = OutputExchange(sum(((n * 16 + 255) & ~255) for _, n, _ in SHAPES) * layers + 4096)
+            ok = 1
+        except Exception as exc:  # noqa: BLE001
+            exchange_note = "output exchange unavailable (%s): NCCL all-gather instead" % str(exc)[:120]
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            if exchange is not None:
+                exchange.close()
+            exchange = None
+            exchange_note = exchange_note or "output exchange unavailable on another rank: NCCL all-gather instead"
     projections = []  # (lin, x, y_local, y_full, n_full, k)
     total_weight = 0
     total_alg = 0
@@ -403,6 +417,7 @@ def run_ours(args) -> dict | None:
                             else "N-sharded x%d + NCCL all-gather" % world) if world > 1 else "single GPU",
             "launch": "CUDA graph" if graph is not None else "eager",
         },
+        **({"note": exchange_note} if exchange_note else {}),
         "us_per_layer": ms_per_step * 1e3 / layers,
         "pct_of_hbm_peak": {"measured_%d" % int(peak): 100.0 * value / world / peak, "nominal_8000": 100.0 * value / world / 8000.0},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
