@@ -444,17 +444,19 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   cp_async_wait<0>();
   if (a.world > 0) {
     // This CTA's rows are on their way to every rank; the last CTA of the launch announces them.
-    // One thread fences for the CTA (the barrier orders the other threads' stores before it), at
-    // system scope, so the rows have landed everywhere before the CTA counts itself done. The CTA
-    // that counts last has therefore seen every CTA's rows land and needs no further fence before
-    // it raises the arrival words (a system-scope fence costs microseconds).
+    // One thread fences for the CTA (the barrier orders the other threads' stores before it) at
+    // device scope and counts the CTA done; the CTA that counts last has thereby synchronised
+    // with every other CTA, so its one system-scope fence covers all their rows (fences are
+    // cumulative) before it raises the arrival words. A system-scope fence in every CTA, with its
+    // own stores still in flight, measured 1.6 us slower per launch.
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      __threadfence();
       const unsigned before = atomicAdd(a.done, 1u);
       if (before == gridDim.x - 1) {
         *reinterpret_cast<volatile unsigned *>(a.done) = 0u;  // for the next launch on this stream
         *reinterpret_cast<volatile unsigned *>(a.launch_no) = previous_launch + 1u;
+        __threadfence_system();
         for (int q = 0; q < a.world; ++q) st_relaxed_sys(a.peer_flags[q] + a.rank, previous_launch + 1u);
       }
     }
