@@ -133,3 +133,21 @@ def test_host_buffer_entry_points_agree():
         y2 = np.empty((x.shape[0], n), dtype=np.float16)
         lin.apply_host(x, y2)
         assert np.array_equal(y2.view(np.uint16), w.numpy().view(np.uint16))
+
+
+@pytest.mark.parametrize("plan", ["1,2,1", "1,3,2", "2,1,2", "2,2,4", "3,1,2", "4,2,2", "5,1,4", "8,1,4"])
+def test_every_launch_plan_gives_the_same_product(plan, monkeypatch):
+    """The warp-level kernel under forced launch plans (K split = cluster size, units per warp,
+    panels in parallel), on a shape with a ragged last panel and an uneven K split."""
+    monkeypatch.setenv("ISHI_FRAG_PLAN", plan)
+    rng = np.random.default_rng(21)
+    n, k = 1000, 5120 + 256
+    blocks = synth.q4k_blocks(rng, n, k)
+    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks), GGMLType.q4K, (n, k)))
+    for m in (1, 8, 11):
+        x = synth.activations(rng, m, k)
+        got = lin(dev(x)).cpu().numpy()
+        want32, _ = oracle.ggml_matmul(int(GGMLType.q4K), blocks, x, n)
+        err = float(np.abs(got.astype(np.float64) - want32.astype(np.float64)).max() / np.abs(want32).max())
+        assert err < 2e-3, (plan, m, err)
+    lin.ctx.poll()
