@@ -32,7 +32,18 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-SHAPES = [("gate", 17408, 5120), ("up", 17408, 5120), ("down", 5120, 17408)]  # (name, N, K)
+MLP_SHAPES = [("gate", 17408, 5120), ("up", 17408, 5120), ("down", 5120, 17408)]  # (name, N, K)
+# --workload stack: all seven projections of a 27B layer (the full verify stack is 64 such layers)
+STACK_SHAPES = [("q", 6144, 5120), ("k", 1024, 5120), ("v", 1024, 5120), ("o", 5120, 6144)] + MLP_SHAPES
+# which projections wait for the other ranks' previous exchange (N > 1): those whose input is made
+# from exchanged outputs. q and gate read the block input (the previous down / o output); k, v and
+# up read what q / gate already waited for; o reads the attention output, down reads gate and up.
+STACK_WAITS = "1001101"
+SHAPES = MLP_SHAPES
+WORKLOAD_NAME = {
+    "mlp": "GGUF Q4_K MLP projections of a 27B model (K=5120/N=17408, K=17408/N=5120), M=8",
+    "stack": "GGUF Q4_K q/k/v/o/gate/up/down projections of a 27B layer (the verify stack is 64 such layers), M=8",
+}
 Q4_K = 12
 ROWS = 8
 METRIC = "quantized-matmul weight GB/s (% of HBM peak) at M=1/8 draft rows; µs/layer"
@@ -155,13 +166,12 @@ def run_reference(args) -> dict:
     t = sum(cpu_pass(layer) for _ in range(steps))
     value = bytes_per_pass * steps / t / 1e9
     cores = oracle.threads()
-    sample = "one MLP block (gate, up, down) at M=8 per step, dequantize-on-the-fly + fp32-exact products"
+    sample = "one block of the workload at M=8 per step, dequantize-on-the-fly + fp32-exact products"
     return {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": t / steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u8/f16 in, f32 accumulate", "data": "synthetic", "impl": "reference",
-        "config": {"workload": "GGUF Q4_K MLP projections of a 27B model (K=5120/N=17408, K=17408/N=5120), M=8",
-                   "layers": 1, "rows": ROWS},
+        "config": {"workload": WORKLOAD_NAME[args.workload], "layers": 1, "rows": ROWS},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -304,7 +314,7 @@ def run_ours(args) -> dict | None:
     # Which projections wait for the other ranks' previous exchange, in the order gate, up, down:
     # gate reads the previous block's down output and down reads gate and up, so both wait; up reads
     # what gate already waited for. ISHI_BENCH_WAITS=111 makes every projection wait, 000 none.
-    WAITS = [c == "1" for c in os.environ.get("ISHI_BENCH_WAITS", "101")]
+    WAITS = [c == "1" for c in os.environ.get("ISHI_BENCH_WAITS", STACK_WAITS if args.workload == "stack" else "101")]
     waits_seen = []
 
     def one_pass():
@@ -312,7 +322,7 @@ def run_ours(args) -> dict | None:
             if exchange is not None:
                 # every kernel stores its rows into all ranks' copies and waits for the other
                 # ranks' previous projection first, as a layer stack's data flow would make it
-                exchange.apply(lin, x, y_local, n_lo, wait_previous=WAITS[len(waits_seen) % 3])
+                exchange.apply(lin, x, y_local, n_lo, wait_previous=WAITS[len(waits_seen) % len(WAITS)])
                 waits_seen.append(0)
             elif world > 1:
                 lin(x, transposed=True, out=y_local)
@@ -410,7 +420,7 @@ def run_ours(args) -> dict | None:
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u8/f16 in, f32 accumulate", "data": "synthetic",
         "config": {
-            "workload": "GGUF Q4_K MLP projections of a 27B model (K=5120/N=17408, K=17408/N=5120), M=8",
+            "workload": WORKLOAD_NAME[args.workload],
             "layers": layers, "rows": ROWS, "l2": "every projection has its own weights: %.2f GB per step" %
             (total_weight / 1e9),
             "parallelism": ("N-sharded x%d, outputs exchanged by the product kernels over NVLink" % world if exchange is not None
@@ -419,16 +429,17 @@ def run_ours(args) -> dict | None:
         },
         **({"note": exchange_note} if exchange_note else {}),
         "us_per_layer": ms_per_step * 1e3 / layers,
+        **({"us_per_64_layer_stack": ms_per_step * 1e3 / layers * 64} if args.workload == "stack" else {}),
         "pct_of_hbm_peak": {"measured_%d" % int(peak): 100.0 * value / world / peak, "nominal_8000": 100.0 * value / world / 8000.0},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if world == 1 and args.workload == "mlp" else None,
                      "kernel": "frag_kernel<FragQ4K, 0>", "peak_kind": peak_kind},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
     if e2e is not None:
         out["e2e"] = e2e
-    if world == 1 and os.environ.get("ISHI_BENCH_NO_FORMATS") != "1":
+    if world == 1 and args.workload == "mlp" and os.environ.get("ISHI_BENCH_NO_FORMATS") != "1":
         out["formats"] = format_table(peak)
     if world == 1:
         layer = cpu_sample()
@@ -455,8 +466,13 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--workload", default="mlp", choices=["mlp", "stack"],
+                    help="mlp: gate/up/down (the headline); stack: all seven projections of a layer")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
+    if args.workload == "stack":
+        global SHAPES
+        SHAPES = STACK_SHAPES
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
