@@ -133,7 +133,9 @@ ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_h
 /* ---- kernel level ------------------------------------------------------------------------- */
 
 /* GGMLKernels.matvec (Sources/IshizukiKit/Core/GGMLKernels.swift:177-213): x [rows, k] against
- * the blocks of w [n, k], CUDA-core FMA with warp-shuffle reductions. rows in 1...16. */
+ * the blocks of w [n, k]. A single row of a format the warp-level kernel decodes (Q4_K) runs on
+ * CUDA cores (fp32 FMA, warp-shuffle reduction); more rows, and the other formats, run the
+ * tensor-core kernel, which is the faster one on this GPU at every row count. rows in 1...16. */
 ishi_status ishi_ggml_matvec(ishi_ctx *ctx, const void *x_dev, int rows, const void *blocks_dev,
                              int64_t blocks_bytes, int ggml_type, int64_t n, int64_t k,
                              void *y_dev, void *stream);
