@@ -15,7 +15,7 @@
 
 namespace ishi {
 
-__constant__ uint16_t c_iq2xs_codes[512];
+static __constant__ uint16_t c_iq2xs_codes[512] = {ISHI_IQ2XS_CODES_LIST};
 
 template <typename OT>
 __device__ __forceinline__ OT to_out(float v);
@@ -116,7 +116,7 @@ __device__ __forceinline__ float load_scale(const void *p, long long i, int dtyp
   return ((const float *)p)[i];
 }
 
-__global__ void __launch_bounds__(256) affine_dequantize_kernel(const uint32_t *__restrict__ w,
+static __global__ void __launch_bounds__(256) affine_dequantize_kernel(const uint32_t *__restrict__ w,
                                                                 const void *__restrict__ scales,
                                                                 const void *__restrict__ biases,
                                                                 int scale_dtype, int group_size, int bits,
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(256) affine_dequantize_kernel(const uint32_t *
 // One CTA per (row, block); the radix-2 stages run in shared memory exactly in the order of the
 // reference's fused kernel (Sources/IshizukiKit/Core/FusedHadamard.swift:54-78) so the fp32
 // roundings agree.
-__global__ void __launch_bounds__(256) hadamard_rotate_kernel(const __half *__restrict__ x, long long width,
+static __global__ void __launch_bounds__(256) hadamard_rotate_kernel(const __half *__restrict__ x, long long width,
                                                               int block, const float *__restrict__ signs,
                                                               __half *__restrict__ y) {
   extern __shared__ float tile[];

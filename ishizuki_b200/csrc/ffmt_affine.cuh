@@ -28,7 +28,7 @@
 
 namespace ishi {
 
-template <int BITS, int GS>
+template <int BITS, int GS, bool BF16>
 struct FragAffine {
   static_assert(BITS == 4 || BITS == 2, "4- and 2-bit codes");
   static_assert(GS == 32 || GS == 64 || GS == 128, "group sizes of the reference");
@@ -51,14 +51,18 @@ struct FragAffine {
       if (row >= s.N) return 0;
       const int q = 2 * c + ((h & 3) >> 1);
       const long long word = (long long)u * (8 * BITS) + 4 * q + t;
-      return *reinterpret_cast<const uint16_t *>(s.w + row * s.w_row_bytes + word * 4 + 2 * (h & 1));
+      long long local;
+      const int seg = frag_segment(s, row, &local);
+      return *reinterpret_cast<const uint16_t *>(s.w[seg] + local * s.w_row_bytes + word * 4 + 2 * (h & 1));
     }
     const int idx = hw - kHeader / 2;
     const long long row = p * kFragRows + idx / (2 * kGroups);
     const int j = idx % (2 * kGroups);
     if (row >= s.N) return 0;
-    const uint8_t *base = j < kGroups ? s.scales : s.biases;
-    return *reinterpret_cast<const uint16_t *>(base + row * s.s_row_bytes + ((long long)u * kGroups + (j % kGroups)) * 2);
+    long long local;
+    const int seg = frag_segment(s, row, &local);
+    const uint8_t *base = j < kGroups ? s.scales[seg] : s.biases[seg];
+    return *reinterpret_cast<const uint16_t *>(base + local * s.s_row_bytes + ((long long)u * kGroups + (j % kGroups)) * 2);
   }
 
   // x * 2^-e on both halves (exact power-of-two scaling)
@@ -74,7 +78,10 @@ struct FragAffine {
   // row): lane l loads the eight values k = 8l .. 8l + 7. The fragment of k-step st = kMasks * q + m
   // sits at st * 256 + ((g ^ (q & 3)) * 4 + t) * 8: the xor spreads a store's quads over the banks,
   // and a k-step's 32 lanes still read one 256-byte run.
-  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc) {
+  // after_loads() runs once, when the first batch of loads is in flight and before their values are
+  // used (the kernel issues its first weight copies there, behind the activations).
+  template <class F>
+  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int tasks = uc * 8;
     constexpr int kBatch = 8;
@@ -88,6 +95,7 @@ struct FragAffine {
         if (i < tasks && (i & 7) < a.M)
           v[e] = __ldg(reinterpret_cast<const uint4 *>(xl + (long long)(i & 7) * a.K + (i >> 3) * 256));
       }
+      if (i0 == warp) after_loads();
 #pragma unroll
       for (int e = 0; e < kBatch; ++e) {
         const int i = i0 + e * nw;
@@ -141,9 +149,9 @@ struct FragAffine {
     }
   }
 
-  static __device__ __forceinline__ float param(uint32_t pair, int hi, int dtype) {
-    const uint32_t h = hi ? pair >> 16 : pair & 0xffffu;
-    return dtype == 0 ? half_bits_to_float(h) : bf16_bits_to_float(h);
+  static __device__ __forceinline__ float param(uint32_t pair, int hi) {
+    if (BF16) return hi ? __uint_as_float(pair & 0xffff0000u) : __uint_as_float(pair << 16);
+    return half_bits_to_float(hi ? pair >> 16 : pair & 0xffffu);
   }
   static __device__ __forceinline__ float half_lo(uint32_t pair) { return __half2float(__ushort_as_half((unsigned short)(pair & 0xffffu))); }
   static __device__ __forceinline__ float half_hi(uint32_t pair) { return __half2float(__ushort_as_half((unsigned short)(pair >> 16))); }
@@ -203,10 +211,10 @@ struct FragAffine {
         if (((q + 1) * kQuadK) % GS == 0) {
           // the group is complete: scale its code sum, add bias times the group's sum of x
           const int grp = (q * kQuadK) / GS;
-          const float s0 = param(hdr0[grp >> 1], grp & 1, a.scale_dtype) * 16777216.f;
-          const float s1 = param(hdr1[grp >> 1], grp & 1, a.scale_dtype) * 16777216.f;
-          const float b0 = param(hdr0[(kGroups + grp) >> 1], (kGroups + grp) & 1, a.scale_dtype);
-          const float b1 = param(hdr1[(kGroups + grp) >> 1], (kGroups + grp) & 1, a.scale_dtype);
+          const float s0 = param(hdr0[grp >> 1], grp & 1) * 16777216.f;
+          const float s1 = param(hdr1[grp >> 1], grp & 1) * 16777216.f;
+          const float b0 = param(hdr0[(kGroups + grp) >> 1], (kGroups + grp) & 1);
+          const float b1 = param(hdr1[(kGroups + grp) >> 1], (kGroups + grp) & 1);
           if (MODE == 0) {
             const float2 xs = lds64f(xu + kSums + (uint32_t)(grp * 8 + 2 * t) * 4u);
             acc[0] += s0 * part[0] + b0 * xs.x;

@@ -41,7 +41,9 @@ struct FragQ4K {
     }
     const long long row = p * kFragRows + row_in_panel;
     if (row >= s.N) return 0;
-    return *reinterpret_cast<const uint16_t *>(s.w + row * s.w_row_bytes + (long long)u * 144 + off);
+    long long local;
+    const int seg = frag_segment(s, row, &local);
+    return *reinterpret_cast<const uint16_t *>(s.w[seg] + local * s.w_row_bytes + (long long)u * 144 + off);
   }
 
   // Activations of the CTA's column range into fragment order. A warp task is (unit, activation
@@ -49,7 +51,10 @@ struct FragQ4K {
   // j = l / 8, half h = (l / 4) % 2, t = l % 4), so a task is one contiguous 512-byte read. The
   // fragment of k-step st = 4j + 2h + s sits at st * 256 + ((g ^ j) * 4 + t) * 8: the xor spreads
   // the four chunks of a store over the banks, and a k-step's 32 lanes still read one 256-byte run.
-  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc) {
+  // after_loads() runs once, when the first batch of loads is in flight and before their values are
+  // used (the kernel issues its first weight copies there, behind the activations).
+  template <class F>
+  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int tasks = uc * 8;
     constexpr int kBatch = 8;
@@ -64,6 +69,7 @@ struct FragQ4K {
         if (i < tasks && (i & 7) < a.M)
           v[e] = __ldg(reinterpret_cast<const uint4 *>(xl + (long long)(i & 7) * a.K + (i >> 3) * 256));
       }
+      if (i0 == warp) after_loads();
 #pragma unroll
       for (int e = 0; e < kBatch; ++e) {
         const int i = i0 + e * nw;

@@ -14,16 +14,18 @@
 
 #include "../../include/ishizuki_cuda.h"
 #include "dequant.cuh"
-#include "ffmt_affine.cuh"
-#include "ffmt_q4k.cuh"
-#include "ishi_fragstream.cuh"
-#include "ishi_rowstream.cuh"
-#include "rfmt_affine.cuh"
-#include "rfmt_iq2xs.cuh"
-#include "rfmt_q4k.cuh"
-#include "rfmt_q6k.cuh"
+#include "ishi_kernels.h"
 
 using namespace ishi;
+
+namespace ishi {
+// the per-format kernel tables (frag_*.cu, row_*.cu)
+const FragOps *frag_ops_q4k();
+const FragOps *frag_ops_affine4(int group_size, bool bf16);
+const FragOps *frag_ops_affine2(int group_size, bool bf16);
+const RowOps *row_ops_ggml(int type);
+const RowOps *row_ops_affine(int bits);
+}  // namespace ishi
 
 namespace {
 
@@ -51,8 +53,8 @@ struct RowPlan {
 // Launch plan of the warp-level kernel (fragment-order tiles, 16-row panels, clusters of S CTAs).
 struct FragPlan {
   bool ok = false;
-  int fmt_id = -1;  // see frag_format()
-  int units = 0, S = 1, P = 0, NC = 1, Wu = 1, PP = 1, SPW = 1, umax = 0, tile_bytes = 0;
+  const FragOps *ops = nullptr;  // the format's kernels
+  int units = 0, S = 1, P = 0, NC = 1, Wu = 1, PP = 1, G = 1, umax = 0, tile_bytes = 0;
   size_t smem = 0, tiles_bytes = 0;
   double cost = 0;
 };
@@ -157,6 +159,8 @@ ishi_status check_desc(ishi_ctx *ctx, const ishi_weight_desc &d, int64_t *weight
   return ISHI_OK;
 }
 
+const RowOps *row_ops(int fmt) { return fmt >= 100 ? row_ops_affine(fmt - 100) : row_ops_ggml(fmt); }
+
 // Sections of a tile for each format: which field of the source goes where.
 void describe_sections(const ishi_weight_desc &d, RowPlan *pl) {
   const uint8_t *w = static_cast<const uint8_t *>(d.weight_dev);
@@ -214,7 +218,9 @@ bool make_row_plan(const ishi_ctx *ctx, const ishi_weight_desc &d, RowPlan *pl) 
   pl->units = (int)(d.k / 256);
   pl->P = (int)((d.n + kRowPanel - 1) / kRowPanel);
   pl->grid = 2 * ctx->sm_count;
-  pl->table_bytes = (d.kind == ISHI_KIND_GGML && d.ggml_type == ISHI_GGML_IQ2_XS) ? RowIQ2XS::kTableBytes : 0;
+  const RowOps *rops = row_ops(format_of(d));
+  if (!rops) return false;
+  pl->table_bytes = rops->table_bytes;
   pl->tiles_bytes = (size_t)pl->P * pl->units * pl->tile_bytes;
   const size_t half_sm = (size_t)(std::min(kSmemPerSm, ctx->smem_optin) - 4096) / 2;
   const size_t fixed = 128 + (size_t)pl->table_bytes;
@@ -283,31 +289,26 @@ ishi_status tile_weight(ishi_ctx *ctx, const RowPlan &pl, long long n, uint8_t *
   return ISHI_OK;
 }
 
-template <class Fmt, int MC>
-ishi_status launch_row_mc(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
-  auto kern = rowstream_kernel<Fmt, MC>;
-  static bool configured[64] = {false};  // per device, per kernel instantiation
+// Raises a kernel family's shared-memory limit once per device.
+ishi_status configure_once(ishi_ctx *ctx, const void *key, cudaError_t (*configure)(int), int max_smem) {
+  static std::map<std::pair<const void *, int>, bool> done;
   static std::mutex once;
-  {
-    std::lock_guard<std::mutex> g(once);
-    if (!configured[ctx->device & 63]) {
-      ISHI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (std::min(kSmemPerSm, ctx->smem_optin) - 4096) / 2));
-      configured[ctx->device & 63] = true;
-    }
+  std::lock_guard<std::mutex> g(once);
+  bool &flag = done[std::make_pair(key, ctx->device)];
+  if (!flag) {
+    ISHI_CUDA(ctx, configure(max_smem));
+    flag = true;
   }
-  kern<<<pl.grid, kRowThreads, pl.smem, st>>>(args);
-  ISHI_CUDA(ctx, cudaGetLastError());
   return ISHI_OK;
 }
 
-// Picks the kernel instance that keeps as many accumulator columns as there are activation rows.
-template <class Fmt>
-ishi_status launch_row(ishi_ctx *ctx, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
-  if (args.M <= 1) return launch_row_mc<Fmt, 1>(ctx, pl, args, st);
-  if (args.M <= 2) return launch_row_mc<Fmt, 2>(ctx, pl, args, st);
-  if (args.M <= 4) return launch_row_mc<Fmt, 4>(ctx, pl, args, st);
-  return launch_row_mc<Fmt, 8>(ctx, pl, args, st);
+ishi_status launch_row(ishi_ctx *ctx, int fmt, const RowPlan &pl, const RowArgs &args, cudaStream_t st) {
+  const RowOps *ops = row_ops(fmt);
+  if (!ops) return fail(ctx, ISHI_E_UNSUPPORTED, "no kernel for format %d", fmt);
+  ishi_status s = configure_once(ctx, ops, ops->configure, (std::min(kSmemPerSm, ctx->smem_optin) - 4096) / 2);
+  if (s != ISHI_OK) return s;
+  ISHI_CUDA(ctx, ops->launch(args.M, pl.grid, pl.smem, args, st));
+  return ISHI_OK;
 }
 
 // One launch: x [rows <= 8, k] against the tiled weight.
@@ -343,15 +344,7 @@ ishi_status run_row(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int f
   a.group_size = d.group_size;
   a.scale_dtype = d.scale_dtype;
   a.bits = d.bits;
-  switch (fmt) {
-    case ISHI_GGML_Q4_K: return launch_row<RowQ4K>(ctx, pl, a, st);
-    case ISHI_GGML_Q6_K: return launch_row<RowQ6K>(ctx, pl, a, st);
-    case ISHI_GGML_IQ2_XS: return launch_row<RowIQ2XS>(ctx, pl, a, st);
-    case 102: return launch_row<RowAffine<2>>(ctx, pl, a, st);
-    case 104: return launch_row<RowAffine<4>>(ctx, pl, a, st);
-    case 108: return launch_row<RowAffine<8>>(ctx, pl, a, st);
-    default: return fail(ctx, ISHI_E_UNSUPPORTED, "no kernel for format %d", fmt);
-  }
+  return launch_row(ctx, fmt, pl, a, st);
 }
 
 // rows 1...16: one launch for up to eight rows, two for more (the weight then streams twice).
@@ -369,92 +362,44 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
 
 // ---- warp-level kernel: plan, tiling, launch ------------------------------------------------------
 
-// Which fragment decoder serves a weight, or -1 (the tcgen05 kernel then takes it).
-int frag_format(const ishi_weight_desc &d) {
-  if (d.kind == ISHI_KIND_GGML) return d.ggml_type == ISHI_GGML_Q4_K ? 0 : -1;
-  if (d.scale_dtype != ISHI_DT_F16 && d.scale_dtype != ISHI_DT_BF16) return -1;
-  if (d.bits == 4) return d.group_size == 32 ? 1 : d.group_size == 64 ? 2 : d.group_size == 128 ? 3 : -1;
-  if (d.bits == 2) return d.group_size == 64 ? 4 : d.group_size == 128 ? 5 : -1;
-  return -1;
-}
-
-template <class T>
-struct FragTag {
-  typedef T type;
-};
-
-// calls f(FragTag<decoder>) for the decoder of fmt_id
-template <class F>
-auto with_frag_format(int fmt_id, F &&f) {
-  switch (fmt_id) {
-    case 1: return f(FragTag<FragAffine<4, 32>>());
-    case 2: return f(FragTag<FragAffine<4, 64>>());
-    case 3: return f(FragTag<FragAffine<4, 128>>());
-    case 4: return f(FragTag<FragAffine<2, 64>>());
-    case 5: return f(FragTag<FragAffine<2, 128>>());
-    default: return f(FragTag<FragQ4K>());
-  }
-}
-
-template <class Fmt, int MODE>
-ishi_status configure_frag(ishi_ctx *ctx) {
-  static bool configured[64] = {false};
-  static std::mutex once;
-  std::lock_guard<std::mutex> g(once);
-  if (!configured[ctx->device & 63]) {
-    ISHI_CUDA(ctx, cudaFuncSetAttribute(frag_kernel<Fmt, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        std::min(kSmemPerSm, ctx->smem_optin) - 1024));
-    configured[ctx->device & 63] = true;
-  }
-  return ISHI_OK;
+// The fragment decoder that serves a weight, or null (the tcgen05 kernel then takes it).
+const FragOps *frag_ops_for(const ishi_weight_desc &d) {
+  if (d.kind == ISHI_KIND_GGML) return d.ggml_type == ISHI_GGML_Q4_K ? frag_ops_q4k() : nullptr;
+  if (d.scale_dtype != ISHI_DT_F16 && d.scale_dtype != ISHI_DT_BF16) return nullptr;
+  const bool bf16 = d.scale_dtype == ISHI_DT_BF16;
+  if (d.bits == 4) return frag_ops_affine4(d.group_size, bf16);
+  if (d.bits == 2) return frag_ops_affine2(d.group_size, bf16);
+  return nullptr;
 }
 
 // how many clusters of s CTAs with this much shared memory the device runs at once
-template <class Fmt>
-int max_frag_clusters(ishi_ctx *ctx, int fmt_id, int s, int warps, size_t smem) {
-  if (s == 1) return ctx->sm_count;
-  static std::map<std::tuple<int, int, int, int, size_t>, int> cache;
+int max_frag_clusters(ishi_ctx *ctx, const FragOps *ops, int s, int warps, size_t smem) {
+  static std::map<std::tuple<int, const void *, int, int, size_t>, int> cache;
   static std::mutex lock;
   std::lock_guard<std::mutex> g(lock);
-  const auto key = std::make_tuple(ctx->device, fmt_id, s, warps, smem);
+  const auto key = std::make_tuple(ctx->device, (const void *)ops, s, warps, smem);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)(s * ctx->sm_count), 1, 1);
-  cfg.blockDim = dim3((unsigned)(warps * 32), 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cudaLaunchAttribute at;
-  at.id = cudaLaunchAttributeClusterDimension;
-  at.val.clusterDim.x = (unsigned)s;
-  at.val.clusterDim.y = 1;
-  at.val.clusterDim.z = 1;
-  cfg.attrs = &at;
-  cfg.numAttrs = 1;
-  int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, frag_kernel<Fmt, 0>, &cfg) != cudaSuccess) {
-    cudaGetLastError();
-    n = 0;
-  }
+  const int n = ops->max_clusters(s, warps, smem, ctx->sm_count);
   cache[key] = n;
   return n;
 }
 
-// Picks the K split S (= cluster size), the warps per panel, the panels a CTA works on in
-// parallel and the panels per group. The estimate counts tile times on the longest warp (panels of
-// the fullest cluster x units per warp), stretched where the warps outnumber what the issue slots
-// sustain.
-template <class Fmt>
-bool make_frag_plan_for(ishi_ctx *ctx, const ishi_weight_desc &d, int fmt_id, FragPlan *pl) {
-  if (configure_frag<Fmt, 0>(ctx) != ISHI_OK || configure_frag<Fmt, 1>(ctx) != ISHI_OK) return false;
-  const int xbytes = Fmt::kXBytes;
+// Picks the K split S (= cluster size), the warps per panel and the panels a CTA works on in
+// parallel. The estimate counts tile times on the longest warp (panels of the fullest cluster x
+// units per warp), stretched where the warps outnumber what the issue slots sustain.
+bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
+  const FragOps *ops = frag_ops_for(d);
+  if (!ops) return false;
+  const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
+  if (configure_once(ctx, ops, ops->configure, (int)budget) != ISHI_OK) return false;
+  const int xbytes = ops->x_bytes;
   FragPlan best;
-  const int tile_bytes = Fmt::kTileBytes;
+  const int tile_bytes = ops->tile_bytes;
   const int units = (int)(d.k / 256);
   const int P = (int)((d.n + kFragRows - 1) / kFragRows);
   // the kernel divides by multiplication, exact while (clusters + 1) * P < 2^32 / clusters
   if ((long long)P * (ctx->sm_count + 1) * ctx->sm_count >= (1ll << 32)) return false;
-  const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
   const char *force = getenv("ISHI_FRAG_PLAN");  // "S,per,PP" for tuning runs
   int fs = 0, fper = 0, fpp = 0;
   if (force) sscanf(force, "%d,%d,%d", &fs, &fper, &fpp);
@@ -465,9 +410,10 @@ bool make_frag_plan_for(ishi_ctx *ctx, const ishi_weight_desc &d, int fmt_id, Fr
     for (int per = per_min; per <= std::min(per_min + 2, kFragGroup); ++per) {
       if (fper && per != fper) continue;
       const int wu = (umax + per - 1) / per;
-      for (int pp = 1; pp <= 4 && wu * pp <= kFragMaxWarps; pp *= 2) {
+      for (int pp = 1; pp <= 4 && wu * pp <= kFragMaxWarps; ++pp) {
         if (fpp && pp != fpp) continue;
         FragPlan c;
+        c.ops = ops;
         c.units = units;
         c.P = P;
         c.S = s;
@@ -476,19 +422,22 @@ bool make_frag_plan_for(ishi_ctx *ctx, const ishi_weight_desc &d, int fmt_id, Fr
         c.Wu = wu;
         c.PP = pp;
         const int w = wu * pp;
-        for (c.SPW = std::max(1, kFragGroup / per); c.SPW >= 1; --c.SPW) {
-          c.smem = frag_smem_bytes(umax, xbytes, w, pp, c.SPW, s, tile_bytes);
+        for (c.G = 2; c.G >= 1; --c.G) {
+          c.smem = frag_smem_bytes(umax, xbytes, w, pp, c.G, s, tile_bytes);
           if (c.smem <= budget) break;
         }
-        if (c.SPW < 1) continue;
+        if (c.G < 1) continue;
         // one CTA per SM: two would stage the activations twice and split the issue slots
-        c.NC = std::min(std::min(max_frag_clusters<Fmt>(ctx, fmt_id, s, w, c.smem), ctx->sm_count / s), P);
+        c.NC = std::min(std::min(max_frag_clusters(ctx, ops, s, w, c.smem), ctx->sm_count / s), P);
         if (c.NC < 1) continue;
+        // Estimate in microseconds, fitted to measurements on the 27B shapes: an SM passes about
+        // 13 tiles per microsecond when enough warps are busy; one warp alone needs about a
+        // microsecond per tile; every panel of a lane costs a reduction over its wu warps.
         const int panels = (P + c.NC - 1) / c.NC;
-        const double tile_time = std::max(1.0, w / 12.0) * (1.0 + 2.0 / w);  // issue-bound past ~12 warps; few warps hide less latency
-        const int rounds = (panels + pp - 1) / pp;                 // panels one warp walks
-        const int groups = (rounds + c.SPW - 1) / c.SPW;            // ... and reductions it takes part in
-        c.cost = (double)rounds * per * tile_time + groups * (0.3 + 0.03 * wu) + 0.05 * umax;
+        const int rounds = (panels + pp - 1) / pp;  // panels one warp walks
+        const double throughput = 0.075 * panels * umax * std::max(1.0, 14.0 / w);
+        const double longest = 1.0 * rounds * per;
+        c.cost = std::max(throughput, longest) + rounds * (0.05 * wu + (s > 1 ? 0.05 : 0.0)) + 0.02 * umax;
         c.ok = true;
         if (!best.ok || c.cost < best.cost) best = c;
       }
@@ -496,70 +445,46 @@ bool make_frag_plan_for(ishi_ctx *ctx, const ishi_weight_desc &d, int fmt_id, Fr
   }
   if (!best.ok) return false;
   best.tiles_bytes = (size_t)P * units * tile_bytes;
-  best.fmt_id = fmt_id;
   if (getenv("ISHI_DEBUG_PLAN"))
-    fprintf(stderr, "ishi plan n=%lld k=%lld: split %d, clusters %d, warps %d x %d, panels per warp and group %d, smem %zu\n",
-            (long long)d.n, (long long)d.k, best.S, best.NC, best.Wu, best.PP, best.SPW, best.smem);
+    fprintf(stderr, "ishi plan n=%lld k=%lld: split %d, clusters %d, warps %d x %d, generation %d, smem %zu\n",
+            (long long)d.n, (long long)d.k, best.S, best.NC, best.Wu, best.PP, best.G, best.smem);
   *pl = best;
   return true;
 }
 
-bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
-  const int fmt_id = frag_format(d);
-  if (fmt_id < 0) return false;
-  return with_frag_format(fmt_id, [&](auto tag) {
-    return make_frag_plan_for<typename decltype(tag)::type>(ctx, d, fmt_id, pl);
-  });
-}
-
-ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weight_desc &d, uint8_t *dst, cudaStream_t st) {
+ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weight_desc *parts, int count, long long n_total,
+                             uint8_t *dst, cudaStream_t st) {
   FragSrc src;
   memset(&src, 0, sizeof(src));
-  src.w = static_cast<const uint8_t *>(d.weight_dev);
-  src.N = d.n;
+  const ishi_weight_desc &d = parts[0];
+  src.N = n_total;
+  src.segments = count;
+  long long row = 0;
+  for (int i = 0; i < count; ++i) {
+    src.w[i] = static_cast<const uint8_t *>(parts[i].weight_dev);
+    src.scales[i] = static_cast<const uint8_t *>(parts[i].scales_dev);
+    src.biases[i] = static_cast<const uint8_t *>(parts[i].biases_dev);
+    src.first_row[i] = row;
+    row += parts[i].n;
+  }
+  for (int i = count; i <= kFragMaxSegments; ++i) src.first_row[i] = row;
   if (d.kind == ISHI_KIND_GGML) {
     src.w_row_bytes = (long long)(d.k / 256) * type_size(d.ggml_type);
   } else {
     src.w_row_bytes = (long long)d.k * d.bits / 8;
-    src.scales = static_cast<const uint8_t *>(d.scales_dev);
-    src.biases = static_cast<const uint8_t *>(d.biases_dev);
     src.group_size = d.group_size;
     src.scale_bytes = 2;
     src.s_row_bytes = (long long)(d.k / d.group_size) * 2;
   }
   const long long total = (long long)pl.P * pl.units * (pl.tile_bytes / 2);
   const int grid = (int)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
-  with_frag_format(pl.fmt_id, [&](auto tag) {
-    prepare_frag_kernel<typename decltype(tag)::type><<<grid, 256, 0, st>>>(src, pl.units, pl.tile_bytes, dst);
-    return 0;
-  });
-  ISHI_CUDA(ctx, cudaGetLastError());
+  ISHI_CUDA(ctx, pl.ops->prepare(src, pl.units, dst, grid, st));
   return ISHI_OK;
 }
 
-template <class Fmt, int MODE>
-ishi_status launch_frag(ishi_ctx *ctx, const FragPlan &pl, const FragArgs &args, bool early, cudaStream_t st) {
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)(pl.NC * pl.S), 1, 1);
-  cfg.blockDim = dim3((unsigned)(pl.Wu * pl.PP * 32), 1, 1);
-  cfg.dynamicSmemBytes = pl.smem;
-  cfg.stream = st;
-  cudaLaunchAttribute at[2];
-  at[0].id = cudaLaunchAttributeClusterDimension;
-  at[0].val.clusterDim.x = (unsigned)pl.S;
-  at[0].val.clusterDim.y = 1;
-  at[0].val.clusterDim.z = 1;
-  // Programmatic dependent launch: the kernel may start while the one before it on the stream
-  // drains. It prefetches weight tiles, which no earlier kernel writes, and waits for the earlier
-  // kernels before it touches x or y. Only for projections, whose tiles were made at create.
-  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = early ? 2 : 1;
-  ISHI_CUDA(ctx, cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, MODE>, args));
-  return ISHI_OK;
-}
+#ifdef ISHI_TRACE
+unsigned long long *g_trace = nullptr;  // diagnostic builds: where the kernels stamp their phases
+#endif
 
 // where a sharded product stores its rows (see ishi_exchange_apply)
 struct PeerOut {
@@ -592,17 +517,20 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.NC = pl.NC;
     a.Wu = pl.Wu;
     a.PP = pl.PP;
-    a.SPW = pl.SPW;
-    a.pp_shift = pl.PP == 4 ? 2 : pl.PP == 2 ? 1 : 0;
+    a.G = pl.G;
     a.inv_s = frag_inverse(pl.S);
     a.inv_nc = frag_inverse(pl.NC);
     a.inv_wu = frag_inverse(pl.Wu);
+    a.inv_pp = frag_inverse(pl.PP);
     a.umax = pl.umax;
     a.group_size = d.group_size;
     a.scale_dtype = d.scale_dtype;
     a.err = ctx->err_dev;
     a.rot_block = rotate ? d.hadamard_block : 0;
     a.rot_signs = rotate ? static_cast<const float *>(d.signs_dev) : nullptr;
+#ifdef ISHI_TRACE
+    a.trace = g_trace;
+#endif
     if (peers) {
       a.world = peers->world;
       a.rank = peers->rank;
@@ -616,12 +544,15 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
       a.wait_previous = peers->wait_previous;
       a.row_offset = peers->row_offset;
     }
-    const bool single = gemv && rows == 1;
-    ishi_status s = with_frag_format(pl.fmt_id, [&](auto tag) {
-      typedef typename decltype(tag)::type Fmt;
-      return single ? launch_frag<Fmt, 1>(ctx, pl, a, early, st) : launch_frag<Fmt, 0>(ctx, pl, a, early, st);
-    });
-    if (s != ISHI_OK) return s;
+    FragLaunch l;
+    l.clusters = pl.NC;
+    l.split = pl.S;
+    l.warps = pl.Wu * pl.PP;
+    l.smem = pl.smem;
+    l.mode = (gemv && rows == 1) ? 1 : 0;
+    l.early = early;
+    l.stream = st;
+    ISHI_CUDA(ctx, pl.ops->launch(l, a));
   }
   return ISHI_OK;
 }
@@ -645,7 +576,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
   if (make_frag_plan(ctx, d, &fp)) {
     s = ensure_workspace(ctx, &ctx->ws, 0, 0, fp.tiles_bytes);
     if (s != ISHI_OK) return s;
-    s = tile_weight_frag(ctx, fp, d, ctx->ws.tiles, st);
+    s = tile_weight_frag(ctx, fp, &d, 1, d.n, ctx->ws.tiles, st);
     if (s != ISHI_OK) return s;
     return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, false, false, st);
   }
@@ -702,6 +633,10 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
 
 extern "C" {
 
+#ifdef ISHI_TRACE
+void ishi_debug_set_trace(void *dev) { g_trace = static_cast<unsigned long long *>(dev); }
+#endif
+
 const char *ishi_status_string(ishi_status s) {
   switch (s) {
     case ISHI_OK: return "ok";
@@ -740,7 +675,6 @@ ishi_status ishi_ctx_create(int device, ishi_ctx **out) {
     *ctx->err_host = 0;
     e = cudaHostGetDevicePointer(&ctx->err_dev, ctx->err_host, 0);
   }
-  if (e == cudaSuccess) e = cudaMemcpyToSymbol(c_iq2xs_codes, ISHI_IQ2XS_CODES, sizeof(ISHI_IQ2XS_CODES));
   if (e != cudaSuccess) {
     if (ctx->err_host) cudaFreeHost(ctx->err_host);
     delete ctx;
@@ -914,7 +848,7 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
   // again afterwards.
   if (make_frag_plan(ctx, p->d, &p->frag)) {
     s = ensure_workspace(ctx, &p->ws, 0, 0, p->frag.tiles_bytes);
-    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, p->d, p->ws.tiles, 0);
+    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, &p->d, 1, p->d.n, p->ws.tiles, 0);
   } else {
     if (!make_row_plan(ctx, p->d, &p->plan)) {
       delete p;

@@ -6,7 +6,7 @@
 // SM's tensor pipe whatever N is (measured for N = 16 ... 128), which caps a few-row product at
 // ~20 weights per clock and SM; eight activation rows fill an m16n8k16 fragment exactly, and the
 // warp-level instruction sustains several times that. The tcgen05 kernel stays for the formats
-// that have no fragment decoder yet.
+// that have no fragment decoder.
 //
 // Layout. The weight is re-tiled once, when the projection is created, into fragment order: a
 // tile is 16 output rows x 256 k (one unit), stored as [16-byte piece][lane] so that every
@@ -18,23 +18,36 @@
 // Work. K is cut into S column ranges and the kernel is launched as thread-block clusters of S
 // CTAs: CTA r of a cluster stages the activations of column range r into shared memory once, in
 // fragment order, and all CTAs of a cluster walk the same run of 16-row panels, dealt to the
-// clusters in equal contiguous runs. Inside a CTA warp w takes the units u = w, w + W, ... of every
-// panel and streams its tiles through a private ring in shared memory with cp.async (16 bytes per
-// lane): no producer warp, no cross-warp wait on the data path. The warps meet once per group of
-// panels (a CTA barrier) to add their partial tiles; the CTA's partial panel then goes into the
-// shared memory of the panel's leader CTA (distributed shared memory), and after a cluster
-// barrier, whose wait is deferred by one group so that it overlaps the next group's tiles, the
-// leader adds the S partials in rank order and writes y. No global scratch, no atomics, every y
-// element written once, the summation order fixed.
+// clusters in equal contiguous runs. A CTA works on PP panels at a time ("panel lanes"), Wu warps
+// per lane: warp (lane wp, position wu) takes panels wp, wp + PP, ... of the cluster's run and in
+// each the units wu, wu + Wu, ... of the CTA's column range, streaming its tiles through a private
+// ring in shared memory: one bulk async copy per tile (the copy engine, not the load/store unit,
+// moves the bytes), completion counted on the ring slot's own mbarrier. No producer warp, no
+// cross-warp wait on the data path.
+//
+// Reduction, without a CTA-wide barrier. A warp that has finished a panel parks its 16 x 8 partial
+// tile in the lane's slot ring and bumps the slot's arrival counter; the warp that arrives last
+// adds the lane's partials in warp order. With S > 1 it sends the CTA's partial panel into the
+// shared memory of the panel's leader CTA (distributed shared memory, st.async counted on an
+// mbarrier there); the leader's last-arriving warp waits for the S partials, adds them in rank
+// order and writes y. Inbox slots are recycled two "generations" (G panels of a lane) later; a
+// relaxed cluster barrier, arrived at the end of a generation and waited for one generation
+// later, tells a sender that every leader is done with the slot it is about to overwrite. No
+// global scratch, no atomics on values, every y element written once, the summation order fixed.
 #pragma once
 #include "ishi_stream.cuh"
 
 namespace ishi {
 
 constexpr int kFragRows = 16;
-constexpr int kFragMaxWarps = 20;
+#ifndef ISHI_FRAG_MAX_WARPS
+#define ISHI_FRAG_MAX_WARPS 20
+#endif
+constexpr int kFragMaxWarps = ISHI_FRAG_MAX_WARPS;  // 20 warps leave 96 registers per thread, 16 warps 128
 constexpr int kFragRing = 3;      // tiles per warp-private ring: two in flight while one is decoded
-constexpr int kFragGroup = 4;     // most panels of one warp between two CTA barriers
+constexpr int kFragGroup = 4;     // most units per warp the planner considers
+constexpr int kFragRed = 2;       // partial-tile slots per panel lane: a warp may run this many panels ahead of the slowest
+constexpr int kFragMaxGen = 4;    // most panels of a lane per generation of inbox slots
 constexpr int kFragMaxSplit = 8;  // portable cluster size
 constexpr int kFragMaxPeers = 8;  // GPUs of one NVSwitch box
 
@@ -46,10 +59,9 @@ struct FragArgs {
   int out_transposed;
   int M, N, K;
   int units, S, P, NC;  // NC clusters of S CTAs
-  int Wu, PP, SPW;      // warps per panel, panels in parallel (1, 2 or 4; Wu * PP warps per CTA), panels per warp and group
-  int pp_shift;         // log2(PP)
-  // ceil(2^32 / d) for d = S, NC, Wu, or 0 for d = 1: see frag_div()
-  unsigned inv_s, inv_nc, inv_wu;
+  int Wu, PP, G;        // warps per panel, panels in parallel (Wu * PP warps per CTA), panels of a lane per inbox generation
+  // ceil(2^32 / d) for d = S, NC, Wu, PP, or 0 for d = 1: see frag_div()
+  unsigned inv_s, inv_nc, inv_wu, inv_pp;
   int umax;             // most units in a column range
   int group_size, scale_dtype;
   int *err;             // raised when a bounded wait gives up
@@ -71,7 +83,36 @@ struct FragArgs {
   unsigned *launch_no;
   int wait_previous;                      // first wait until every rank's previous launch has arrived here
   long long row_offset;
+  unsigned long long *trace;              // diagnostic builds (-DISHI_TRACE): [CTA][warp][32] timestamps, else unused
 };
+
+// Diagnostic builds stamp the global nanosecond timer at the kernel's phase boundaries.
+#ifdef ISHI_TRACE
+#define ISHI_STAMP(slot)                                                                                   \
+  do {                                                                                                     \
+    if (a.trace && lane == 0) {                                                                            \
+      unsigned long long t_;                                                                               \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)::"memory");                                    \
+      a.trace[((size_t)blockIdx.x * kFragMaxWarps + warp) * 32 + (slot)] = t_;                             \
+    }                                                                                                      \
+  } while (0)
+// ... and add up the clock cycles a warp spends in each part of its panel loop (slots 16 ... 23)
+#define ISHI_CLOCK(var) const long long var = clock64()
+#define ISHI_SPENT(slot, from, to)                                                                        \
+  do {                                                                                                     \
+    if (a.trace && lane == 0) a.trace[((size_t)blockIdx.x * kFragMaxWarps + warp) * 32 + (slot)] += (unsigned long long)((to) - (from)); \
+  } while (0)
+#else
+#define ISHI_STAMP(slot) \
+  do {                   \
+  } while (0)
+#define ISHI_CLOCK(var) \
+  do {                  \
+  } while (0)
+#define ISHI_SPENT(slot, from, to) \
+  do {                             \
+  } while (0)
+#endif
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
@@ -128,10 +169,14 @@ __host__ inline unsigned frag_inverse(int d) { return d == 1 ? 0u : (unsigned)((
 __host__ __device__ inline int frag_column_begin(int c, int units, int S) { return (c * units) / S; }
 __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_bytes + 127) & ~127; }
 
-// shared memory of one CTA, in order: activations, partial tiles of the warps, partial panels of
-// the cluster's CTAs, two mbarriers and an abort word, the warps' rings
-__host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int SPW, int S, int tile_bytes) {
-  return (size_t)umax * xbytes + (size_t)W * SPW * 512 + 2 * (size_t)SPW * PP * S * 512 + 128 +
+// shared memory of one CTA, in order: activations, the lanes' partial-tile slots, the inbox for the
+// partial panels of the cluster's CTAs, a control block (inbox mbarriers, arrival counters,
+// progress words, abort word), the warps' rings
+// control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @256, done [PP] @288,
+// abort @304, phases used of every inbox mbarrier [PP][2G] @320, ring mbarriers [warp][kFragRing] @512
+constexpr uint32_t kFragCtrlBytes = 1024;
+__host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int G, int S, int tile_bytes) {
+  return (size_t)umax * xbytes + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
          (size_t)W * kFragRing * frag_ring_stride(tile_bytes);
 }
 
@@ -144,33 +189,41 @@ __device__ __forceinline__ void st_relaxed_sys(unsigned *p, unsigned v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// element idx of panel p in accumulator-fragment order: lane idx / 4 (g = lane / 4, t = lane % 4),
-// register e = idx % 4 -> weight row g + 8 * (e / 2), activation row 2t + e % 2.
-// With an output exchange the 32 lanes of a warp hold 32 consecutive elements (two weight rows
-// g, two rows g + 8, eight activation rows each): they gather each row's eight values in one lane,
-// which stores the 16 bytes into every rank's copy.
-__device__ __forceinline__ void frag_write(const FragArgs &a, int p, int idx, float v) {
+// One lane's part of panel p's finished 16 x 8 tile, in accumulator-fragment order: lane
+// (g = lane / 4, t = lane % 4) holds v.x, v.y = weight row g, activation rows 2t, 2t + 1 and
+// v.z, v.w = weight row g + 8, the same activation rows. Called by all 32 lanes of a warp.
+// With an output exchange the four lanes of a weight row gather its eight values and one of them
+// stores the 16 bytes into every rank's copy.
+__device__ __forceinline__ void frag_write(const FragArgs &a, int p, int lane, float4 v) {
+  const int g = lane >> 2, t = lane & 3;
+  const long long n0 = (long long)p * kFragRows + g;
   if (a.world > 0) {
-    const uint32_t mine = __half_as_ushort(__float2half_rn(v));
-    const uint32_t pair = mine | (__shfl_down_sync(0xffffffffu, mine, 1) << 16);  // activation rows 2t, 2t + 1 (even idx)
-    const uint32_t w1 = __shfl_down_sync(0xffffffffu, pair, 4), w2 = __shfl_down_sync(0xffffffffu, pair, 8);
-    const uint32_t w3 = __shfl_down_sync(0xffffffffu, pair, 12);
-    if ((idx & 13) == 0) {  // t = 0 and an even register: weight row g + 8 * ((idx >> 1) & 1)
-      const long long n = (long long)p * kFragRows + (idx >> 4) + ((idx & 2) ? 8 : 0);
-      if (n < a.N) {
-        const uint4 row = make_uint4(pair, w1, w2, w3);
-        for (int q = 0; q < a.world; ++q) *reinterpret_cast<uint4 *>(a.peer_y[q] + (a.row_offset + n) * 8) = row;
-      }
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    const uint32_t plo = *reinterpret_cast<const uint32_t *>(&lo), phi = *reinterpret_cast<const uint32_t *>(&hi);
+    const int base = lane & ~3;
+    uint4 rlo, rhi;
+    rlo.x = __shfl_sync(0xffffffffu, plo, base), rlo.y = __shfl_sync(0xffffffffu, plo, base + 1);
+    rlo.z = __shfl_sync(0xffffffffu, plo, base + 2), rlo.w = __shfl_sync(0xffffffffu, plo, base + 3);
+    rhi.x = __shfl_sync(0xffffffffu, phi, base), rhi.y = __shfl_sync(0xffffffffu, phi, base + 1);
+    rhi.z = __shfl_sync(0xffffffffu, phi, base + 2), rhi.w = __shfl_sync(0xffffffffu, phi, base + 3);
+    // lanes t = 0, 1 store row g to the even / odd ranks, lanes t = 2, 3 row g + 8
+    const long long n = n0 + ((t & 2) ? 8 : 0);
+    if (n < a.N) {
+      const uint4 row = (t & 2) ? rhi : rlo;
+      for (int q = t & 1; q < a.world; q += 2) *reinterpret_cast<uint4 *>(a.peer_y[q] + (a.row_offset + n) * 8) = row;
     }
     return;
   }
-  const int ln = idx >> 2, e = idx & 3;
-  const long long n = (long long)p * kFragRows + (ln >> 2) + ((e & 2) ? 8 : 0);
-  const int m = 2 * (ln & 3) + (e & 1);
-  if (n < a.N && m < a.M) {
-    const __half h = __float2half_rn(v);
-    if (a.out_transposed) a.y[n * a.ldy + m] = h;
-    else a.y[(long long)m * a.ldy + n] = h;
+  const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long n = n0 + ((i & 2) ? 8 : 0);
+    const int m = 2 * t + (i & 1);
+    if (n < a.N && m < a.M) {
+      const __half h = __float2half_rn(e[i]);
+      if (a.out_transposed) a.y[n * a.ldy + m] = h;
+      else a.y[(long long)m * a.ldy + n] = h;
+    }
   }
 }
 
@@ -219,23 +272,12 @@ __device__ __forceinline__ uint4 frag_rotate8(uint4 v, int block, const float *s
   return make_uint4(r[0], r[1], r[2], r[3]);
 }
 
-// sum of n <= MAX floats at addr, addr + stride, ...: all loads are issued before the first add, so
-// the latency of shared memory is paid once
-template <int MAX>
-__device__ __forceinline__ float lds_sum_upto(uint32_t addr, uint32_t stride, int n) {
-  float v[MAX];
-#pragma unroll
-  for (int i = 0; i < MAX; ++i) v[i] = i < n ? lds32f(addr + (uint32_t)i * stride) : 0.f;
-#pragma unroll
-  for (int w = 1; w < MAX; w *= 2)
-#pragma unroll
-    for (int i = 0; i + w < MAX; i += 2 * w) v[i] += v[i + w];
-  return v[0];
-}
-__device__ __forceinline__ float lds_sum(uint32_t addr, uint32_t stride, int n) {
-  if (n <= 4) return lds_sum_upto<4>(addr, stride, n);
-  if (n <= 8) return lds_sum_upto<8>(addr, stride, n);
-  return lds_sum_upto<kFragMaxWarps>(addr, stride, n);
+// 16 bytes into another CTA's shared memory; the bytes count as completed on that CTA's mbarrier
+// when they have landed, so the reader needs no fence: it waits for the barrier's phase
+__device__ __forceinline__ void st_async128(uint32_t addr, float4 v, uint32_t mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1,%2,%3,%4}, [%5];" ::"r"(addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(mbar)
+               : "memory");
 }
 
 // MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row.
@@ -247,18 +289,24 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int S = a.S, Wu = a.Wu, PP = a.PP, SPW = a.SPW, pp_shift = a.pp_shift;
-  const int W = Wu * PP, SP = SPW * PP;
-  const int wp = frag_div((unsigned)warp, a.inv_wu), wu = warp - wp * Wu;  // this warp's panel lane and unit lane
+  const int S = a.S, Wu = a.Wu, PP = a.PP, G = a.G;
+  const int W = Wu * PP;
+  // This warp's position wu in its panel lane wp. The lanes are dealt round robin over the warps,
+  // so that with 2 or 4 lanes all warps of an SM sub-partition (warp % 4) belong to one lane: the
+  // scheduler's preference for its oldest warps then cannot starve a whole lane.
+  const int wu = frag_div((unsigned)warp, a.inv_pp), wp = warp - wu * PP;
 
-  const uint32_t xfrag = smem_u32(smem);                          // [umax][Fmt::kXBytes]
-  const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;   // [W][SPW][128 floats]
-  const uint32_t inbox = red + (uint32_t)(W * SPW) * 512u;        // [2][SP][S][128 floats]
-  const uint32_t full = inbox + 2u * (uint32_t)(SP * S) * 512u;   // two mbarriers (one per inbox half), the abort word
-  const uint32_t ring = full + 128u + (uint32_t)warp * kFragRing * kStride;
-  uint64_t *full_p = reinterpret_cast<uint64_t *>(smem + (full - xfrag));
-  volatile int *abort_word = reinterpret_cast<volatile int *>(full_p + 2);
-  const uint32_t ring_end = ring + kFragRing * kStride;
+  const uint32_t xfrag = smem_u32(smem);                                   // [umax][Fmt::kXBytes]
+  const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;            // [PP][kFragRed][Wu][128 floats]
+  const uint32_t inbox = red + (uint32_t)(W * kFragRed) * 512u;            // [PP][2G][S][128 floats]
+  const uint32_t ctrl = inbox + (S > 1 ? (uint32_t)(PP * 2 * G * S) * 512u : 0u);
+  const uint32_t ring = ctrl + kFragCtrlBytes + (uint32_t)warp * kFragRing * kStride;
+  uint8_t *ctrl_p = smem + (ctrl - xfrag);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(ctrl_p);                   // [PP][2G]
+  int *cnt = reinterpret_cast<int *>(ctrl_p + 256);                        // [PP][kFragRed] arrivals of the lane's warps
+  volatile int *done = reinterpret_cast<volatile int *>(ctrl_p + 288);     // [PP] panels of the lane whose partials were added
+  volatile int *abort_word = reinterpret_cast<volatile int *>(ctrl_p + 304);
+  volatile int *uses = reinterpret_cast<volatile int *>(ctrl_p + 320);     // [PP][2G] completed phases of each inbox mbarrier
 
   // (divisions by multiplication: the host checks the ranges)
   const int cid = frag_div(blockIdx.x, a.inv_s);
@@ -269,38 +317,49 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   const int pa = frag_div((unsigned)cid * (unsigned)a.P, a.inv_nc);
   const int np = frag_div((unsigned)(cid + 1) * (unsigned)a.P, a.inv_nc) - pa;
   const int per = frag_div((unsigned)(uc - 1 - wu + Wu), a.inv_wu);  // units of a panel this warp owns: wu + i * Wu < uc
-  const int npw = np > wp ? (np - wp + PP - 1) >> pp_shift : 0;           // panels this warp takes: wp, wp + PP, ...
+  const int contributors = min(Wu, uc);                              // warps of a lane that own a unit
+  const int rounds = frag_div((unsigned)(np + PP - 1), a.inv_pp);    // panels of the fullest lane
+  const int npw = np > wp ? frag_div((unsigned)(np - wp + PP - 1), a.inv_pp) : 0;  // panels this warp takes: wp, wp + PP, ...
 
+  ISHI_STAMP(0);
   // Let the next kernel on the stream start its own prologue as SMs fall free.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  // Shared memory of another CTA may be written only once that CTA runs and has set up its
-  // barriers: every CTA arrives here, and waits before the first group.
-  if (S > 1) {
-    if (threadIdx.x == 0) {
-      mbar_init(full_p, 1);
-      mbar_init(full_p + 1, 1);
-      *abort_word = 0;
-      mbar_fence_init();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < PP * 2 * G; ++i) {
+      mbar_init(bars + i, 1);
+      uses[i] = 0;
     }
-    cluster_arrive_relaxed();  // the init fence above is what the peers need; nothing else to publish yet
+    for (int i = 0; i < PP * kFragRed; ++i) cnt[i] = 0;
+    for (int i = 0; i < PP; ++i) done[i] = 0;
+    *abort_word = 0;
+    mbar_fence_init();
   }
+  // Shared memory of another CTA may be written only once that CTA runs and has set up its
+  // barriers: every CTA arrives here, and waits before its first panel.
+  if (S > 1) cluster_arrive_relaxed();  // the init fence above is what the peers need; nothing else to publish yet
 
   // This warp's tile sequence: its panels in order, in each its units wu + qi * Wu. The fetch
-  // cursor runs kFragRing - 1 tiles ahead of the compute cursor.
-  int f_left = npw * per, f_qi = 0;
-  uint32_t f_slot = ring + (uint32_t)lane * 16u;  // this lane's 16 bytes of every 512
-  const uint32_t f_end = ring_end + (uint32_t)lane * 16u;
-  const uint8_t *f_src = a.tiles + ((long long)(pa + wp) * a.units + ub0 + wu) * (long long)kTile + lane * 16;
+  // cursor runs kFragRing - 1 tiles ahead of the compute cursor. Lane 0 issues the copies; every
+  // lane keeps the cursor.
+  const uint32_t wbar = ctrl + 512u + (uint32_t)warp * kFragRing * 8u;  // this warp's ring mbarriers
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < kFragRing; ++i) mbar_init_u32(wbar + 8u * i, 1);
+    mbar_fence_init();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copy engine sees the barriers initialised
+  }
+  __syncwarp();
+  int f_left = npw * per, f_qi = 0, f_idx = 0;
+  uint32_t f_slot = ring;
+  const uint8_t *f_src = a.tiles + ((long long)(pa + wp) * a.units + ub0 + wu) * (long long)kTile;
   const long long step_unit = (long long)Wu * kTile;
   const long long step_panel = ((long long)PP * a.units - (long long)per * Wu) * kTile;
   auto fetch = [&]() {
-    if (f_left > 0) {
-#pragma unroll
-      for (int o = 0; o + 512 <= kTile; o += 512) cp_async16(f_slot + o, f_src + o);
-      if ((kTile & 511) != 0 && lane * 16 < (kTile & 511)) cp_async16(f_slot + (kTile & ~511), f_src + (kTile & ~511));
+    if (f_left > 0 && lane == 0) {
+      mbar_arrive_expect_tx_u32(wbar + 8u * f_idx, (uint32_t)kTile);
+      bulk_g2s_u32(f_slot, f_src, (uint32_t)kTile, wbar + 8u * f_idx);
     }
-    cp_async_commit();  // one group per slot, present or not, so the wait below counts slots
     --f_left;
     f_src += step_unit;
     if (++f_qi == per) {
@@ -308,15 +367,19 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       f_src += step_panel;
     }
     f_slot += kStride;
-    if (f_slot == f_end) f_slot -= kFragRing * kStride;
+    if (++f_idx == kFragRing) {
+      f_idx = 0;
+      f_slot = ring;
+    }
   };
+  // The weight tiles are written by no earlier kernel: their first copies go out at once.
 #pragma unroll
   for (int i = 0; i < kFragRing - 1; ++i) fetch();
 
-  // Everything above reads only the weight tiles. x may be the output of the kernel before this
-  // one and y may still be read by it: wait for the earlier kernels (returns at once unless this
-  // kernel was launched early).
+  // x may be the output of the kernel before this one and y may still be read by it: wait for the
+  // earlier kernels (returns at once unless this kernel was launched early).
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  ISHI_STAMP(1);
   unsigned previous_launch = 0;
   if (a.world > 0) {
     previous_launch = *reinterpret_cast<volatile unsigned *>(a.launch_no);
@@ -333,115 +396,177 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       __syncthreads();
     }
   }
+  ISHI_STAMP(2);
 
-  // activations of the column range into fragment order (all warps), while the first tiles fly
-  Fmt::stage_x(a, xfrag, ub0, uc);
+  // activations of the column range into fragment order (all warps)
+  Fmt::stage_x(a, xfrag, ub0, uc, [&]() { ISHI_STAMP(8); });
+  ISHI_STAMP(3);
   __syncthreads();
+  ISHI_STAMP(4);
   // shared-memory loads are plain asm the compiler may move; tie their addresses to the waits
   const uint32_t xf = stage_acquire(xfrag) + (uint32_t)wu * Fmt::kXBytes;
 
   if (S > 1) cluster_wait_relaxed();
+  ISHI_STAMP(5);
 
-  // the leader of a group's panel pn: rank pn % S
-  auto leader_of = [&](int pn) -> int { return pn - frag_div((unsigned)pn, a.inv_s) * S; };
-  // the leaders' part of group gi: wait for the S partial panels, add them in rank order, write y
-  auto finish_group = [&](int gi) {
-    const uint32_t bar = full + (uint32_t)(gi & 1) * 8u, parity = (uint32_t)(gi >> 1) & 1u;
-    if (!mbar_try_wait_cluster(bar, parity)) {
-      bool ok = false;
-      for (uint32_t i = 0; i < kWaitSpins && !ok; ++i) {
-        ok = mbar_try_wait_cluster(bar, parity);
-        if (!ok && *abort_word != 0) break;
-      }
-      if (!ok) {  // give up: y of this group stays wrong, the error word tells the host
-        *abort_word = 1;
-        *a.err = 1;
-        return;
-      }
-    }
-    const uint32_t ib = stage_acquire(inbox) + (uint32_t)((gi & 1) * SP * S) * 512u;
-    for (int f = threadIdx.x; f < SP * 128; f += blockDim.x) {
-      const int pn = f >> 7, idx = f & 127, pi = gi * SP + pn;
-      if (pi >= np || leader_of(pn) != r) continue;
-      frag_write(a, pa + pi, idx, lds_sum(ib + (uint32_t)(pn * S * 128 + idx) * 4u, 512u, S));
-    }
-  };
-
-  const int ngroups = (np + SP - 1) / SP;
-  uint32_t c_slot = ring;
-  for (int gi = 0; gi < ngroups; ++gi) {
-    // this warp's panels of the group, one after the other; each partial tile goes straight to the
-    // reduction buffer (the barrier at the end of the previous group freed it)
-    for (int k = 0; k < SPW; ++k) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      if (gi * SP + k * PP + wp < np) {
-        uint32_t xq = xf;
-        for (int qi = 0; qi < per; ++qi) {
-          cp_async_wait<kFragRing - 2>();  // this slot has landed (the younger ones may still be in flight)
-          __syncwarp();                    // ... for every lane, and every lane is done with the previous slot
-          fetch();                         // refill the previous slot
-          Fmt::template unit<MODE>(acc, a, stage_acquire(c_slot), xq, g, t, lane);
-          values_ready(acc[0], acc[1], acc[2], acc[3]);
-          xq += (uint32_t)Wu * Fmt::kXBytes;
-          c_slot += kStride;
-          if (c_slot == ring_end) c_slot = ring;
+  int arrived = 0, waited = 0;  // cluster barrier generations this thread has arrived at / waited for
+  int gen = 0, gpos = 0;        // generation of inbox slots, position of the lane's panel in it
+  uint32_t c_slot = ring, c_phase = 0;
+  int c_idx = 0;
+  for (int i = 0; i < rounds; ++i, ++gpos) {
+    if (gpos == G) {
+      gpos = 0;
+      ++gen;
+      if (S > 1) {
+        // generation gen - 1 is finished here; generation gen reuses the inbox slots of gen - 2,
+        // which every leader has read once all warps of the cluster have finished gen - 2
+        if (arrived > waited) {
+          cluster_wait_relaxed();
+          ++waited;
         }
-        if (MODE == 1) {
-          // single activation row: each lane holds partial dot products of rows g (acc[0]) and
-          // g + 8 (acc[2]) over its own k positions; add across the four lanes of a row
-          acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
-          acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
-          acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 1);
-          acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 2);
-          if (t != 0) acc[0] = acc[2] = 0.f;  // one copy per row enters the sums below (column m = 0)
-          acc[1] = acc[3] = 0.f;
-        }
+        cluster_arrive_relaxed();
+        ++arrived;
       }
-      sts128(red + ((uint32_t)(warp * SPW + k) * 32u + lane) * 16u, make_float4(acc[0], acc[1], acc[2], acc[3]));
     }
+    const int pi = wp + i * PP;  // the panel's index in the cluster's run
+    if (pi >= np || per == 0) continue;
 
-    // add the warps' partial tiles (all threads, one output element each)
-    __syncthreads();
-    if (S > 1 && gi > 0) {
-      cluster_wait_relaxed();  // every CTA has read what it led of group gi - 2: that inbox half is free
-      finish_group(gi - 1);
-    }
-    if (S > 1 && threadIdx.x == 0) {
-      // what this CTA will receive for group gi: S partial panels for every panel it leads
-      // (panels r, r + S, ... of the group, as far as the group goes)
-      const int left = min(SP, np - gi * SP);
-      const int led = left > r ? (left - r + S - 1) / S : 0;
-      mbar_arrive_expect_tx(full_p + (gi & 1), (uint32_t)(led * S) * 512u);
-    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     {
-      const uint32_t rbs = stage_acquire(red);
-      for (int f = threadIdx.x; f < SP * 128; f += blockDim.x) {
-        const int pn = f >> 7, idx = f & 127, pi = gi * SP + pn;
-        if (pi >= np) continue;
-        const uint32_t src = rbs + (uint32_t)(((pn & (PP - 1)) * Wu * SPW + (pn >> pp_shift)) * 128 + idx) * 4u;
-        const float sum = lds_sum(src, (uint32_t)SPW * 512u, Wu);
-        if (S == 1) {
-          frag_write(a, pa + pi, idx, sum);
-        } else {
-          const uint32_t lead = (uint32_t)leader_of(pn);
-          const uint32_t mine = inbox + (uint32_t)((((gi & 1) * SP + pn) * S + r) * 128 + idx) * 4u;
-          st_async32(cluster_map(mine, lead), sum, cluster_map(full + (uint32_t)(gi & 1) * 8u, lead));
+      uint32_t xq = xf;
+      for (int qi = 0; qi < per; ++qi) {
+        ISHI_CLOCK(c0);
+        if (!mbar_wait_u32(wbar + 8u * c_idx, c_phase, abort_word)) *a.err = 1;  // this slot has landed
+        __syncwarp();  // every lane is done with the previous slot
+        if (i == 0 && qi == 0) ISHI_STAMP(6);
+        ISHI_CLOCK(c1);
+        fetch();                         // refill the previous slot
+        Fmt::template unit<MODE>(acc, a, stage_acquire(c_slot), xq, g, t, lane);
+        values_ready(acc[0], acc[1], acc[2], acc[3]);
+        ISHI_CLOCK(c2);
+        ISHI_SPENT(16, c0, c1);
+        ISHI_SPENT(17, c1, c2);
+        xq += (uint32_t)Wu * Fmt::kXBytes;
+        c_slot += kStride;
+        if (++c_idx == kFragRing) {
+          c_idx = 0;
+          c_slot = ring;
+          c_phase ^= 1u;
+        }
+      }
+      if (MODE == 1) {
+        // single activation row: each lane holds partial dot products of rows g (acc[0]) and
+        // g + 8 (acc[2]) over its own k positions; add across the four lanes of a row
+        acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+        acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
+        acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 1);
+        acc[2] += __shfl_xor_sync(0xffffffffu, acc[2], 2);
+        if (t != 0) acc[0] = acc[2] = 0.f;  // one copy per row enters the sums below (column m = 0)
+        acc[1] = acc[3] = 0.f;
+      }
+    }
+    if (i == 0) ISHI_STAMP(7);
+
+    // park the partial tile; the warp of the lane that arrives last adds the lane's partials
+    ISHI_CLOCK(c3);
+    float4 sum = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    bool last = true;
+    if (contributors > 1) {
+      const int rs = i & (kFragRed - 1);
+      const uint32_t slot = red + (uint32_t)((wp * kFragRed + rs) * Wu) * 512u;
+      if (i >= kFragRed && done[wp] < i - kFragRed + 1) {
+        // the slot still holds the partials of panel i - kFragRed of this lane
+        bool ok = false;
+        for (uint32_t spin = 0; spin < kWaitSpins && !ok; ++spin) {
+          ok = done[wp] >= i - kFragRed + 1;
+          if (!ok && *abort_word != 0) break;
+        }
+        if (!ok) {
+          *abort_word = 1;
+          *a.err = 1;
+        }
+      }
+      sts128(stage_acquire(slot) + (uint32_t)(wu * 32 + lane) * 16u, sum);
+      __syncwarp();
+      int old = 0;
+      if (lane == 0) {
+        __threadfence_block();
+        old = atomicAdd(cnt + wp * kFragRed + rs, 1);
+      }
+      old = __shfl_sync(0xffffffffu, old, 0);
+      last = old == contributors - 1;
+      if (last) {
+        __threadfence_block();
+        const uint32_t src = stage_acquire(slot) + (uint32_t)lane * 16u;
+        sum = lds128f(src);
+        for (int w = 1; w < contributors; ++w) {
+          const float4 o = lds128f(src + (uint32_t)w * 512u);
+          sum.x += o.x, sum.y += o.y, sum.z += o.z, sum.w += o.w;
+        }
+        values_ready(sum.x, sum.y, sum.z, sum.w);
+        __syncwarp();
+        if (lane == 0) {
+          cnt[wp * kFragRed + rs] = 0;
+          __threadfence_block();
+          done[wp] = i + 1;
         }
       }
     }
-    if (S > 1) cluster_arrive_relaxed();
-    __syncthreads();  // every thread has read the reduction buffer: the next group may write it
-  }
-  if (S > 1) {
-    if (ngroups > 0) {
-      cluster_wait_relaxed();
-      finish_group(ngroups - 1);
+    ISHI_CLOCK(c4);
+    ISHI_SPENT(18, c3, c4);
+    if (!last) continue;
+
+    if (S == 1) {
+      frag_write(a, pa + pi, lane, sum);
+    } else {
+      // the CTA's partial panel goes to the panel's leader, rank pi % S
+      const int lead = pi - frag_div((unsigned)pi, a.inv_s) * S;
+      const int is = wp * 2 * G + (gen & 1) * G + gpos;  // inbox slot
+      const uint32_t bar = ctrl + (uint32_t)is * 8u;
+      const uint32_t box = inbox + (uint32_t)(is * S) * 512u + (uint32_t)lane * 16u;
+      if (lead == r) {
+        if (lane == 0) mbar_arrive_expect_tx(bars + is, (uint32_t)S * 512u);
+        __syncwarp();
+      }
+      st_async128(cluster_map(box + (uint32_t)r * 512u, (uint32_t)lead), sum, cluster_map(bar, (uint32_t)lead));
+      ISHI_CLOCK(c5);
+      ISHI_SPENT(19, c4, c5);
+      if (lead == r) {
+        // a CTA leads only some of the panels that map to this slot, so the barrier's phase is
+        // counted here; the slot's next use is two generations away, behind a cluster barrier
+        const uint32_t parity = (uint32_t)uses[is] & 1u;
+        bool ok = mbar_try_wait_cluster(bar, parity);
+        for (uint32_t spin = 0; spin < kWaitSpins && !ok; ++spin) {
+          ok = mbar_try_wait_cluster(bar, parity);
+          if (!ok && *abort_word != 0) break;
+        }
+        if (!ok) {  // give up: y of this panel stays wrong, the error word tells the host
+          *abort_word = 1;
+          *a.err = 1;
+        } else {
+          const uint32_t src = stage_acquire(box);
+          float4 total = lds128f(src);
+          for (int q = 1; q < S; ++q) {
+            const float4 o = lds128f(src + (uint32_t)q * 512u);
+            total.x += o.x, total.y += o.y, total.z += o.z, total.w += o.w;
+          }
+          frag_write(a, pa + pi, lane, total);
+        }
+        __syncwarp();
+        if (lane == 0) uses[is] = (int)parity + 1;
+        ISHI_CLOCK(c6);
+        ISHI_SPENT(20, c5, c6);
+      }
     }
+  }
+  ISHI_STAMP(24);
+  if (S > 1) {
     // no CTA leaves while another may still send to it or read its barriers
+    if (arrived > waited) cluster_wait_relaxed();
     cluster_arrive_relaxed();
     cluster_wait_relaxed();
   }
-  cp_async_wait<0>();
+  ISHI_STAMP(27);
   if (a.world > 0) {
     // This CTA's rows are on their way to every rank; the last CTA of the launch announces them.
     // One thread fences for the CTA (the barrier orders the other threads' stores before it) at
@@ -464,7 +589,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
 }
 
 // waits (bounded) until every rank's arrival word has reached this rank's latest launch
-__global__ void peer_wait_kernel(const unsigned *local_flags, int world, const unsigned *launch_no, int *err) {
+static __global__ void peer_wait_kernel(const unsigned *local_flags, int world, const unsigned *launch_no, int *err) {
   if ((int)threadIdx.x < world) {
     const unsigned seq = *reinterpret_cast<const volatile unsigned *>(launch_no);
     bool ok = false;
@@ -477,13 +602,26 @@ __global__ void peer_wait_kernel(const unsigned *local_flags, int world, const u
 }
 
 // One-time re-tiling into fragment order: Fmt::tile_halfword says which 2 bytes of the source
-// land at halfword hw of tile (p, u). Rows past N read as zero.
+// land at halfword hw of tile (p, u). Rows past N read as zero. The source may be several weights
+// of the same format and input width stacked along the output rows (projections that share their
+// input, fused into one launch): segment i holds rows first_row[i] ... first_row[i + 1] - 1.
+constexpr int kFragMaxSegments = 4;
 struct FragSrc {
-  const uint8_t *w, *scales, *biases;  // GGUF blocks, or an affine pack's three arrays
+  const uint8_t *w[kFragMaxSegments], *scales[kFragMaxSegments], *biases[kFragMaxSegments];
+  long long first_row[kFragMaxSegments + 1];
+  int segments;
   long long w_row_bytes, s_row_bytes;  // distance between rows
   long long N;
   int group_size, scale_bytes;
 };
+
+// which segment holds output row `row` (< N), and the row's index inside it
+__device__ __forceinline__ int frag_segment(const FragSrc &s, long long row, long long *local) {
+  int i = 0;
+  while (i + 1 < s.segments && row >= s.first_row[i + 1]) ++i;
+  *local = row - s.first_row[i];
+  return i;
+}
 
 template <class Fmt>
 __global__ void __launch_bounds__(256) prepare_frag_kernel(const FragSrc src, int units, int tile_bytes,

@@ -1,0 +1,39 @@
+// What the C-ABI layer knows of the product kernels: one table of plain functions per weight
+// format, defined in that format's own translation unit (frag_*.cu for the warp-level kernel,
+// row_*.cu for the tcgen05 kernel) so that the formats compile side by side.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "ishi_fragstream.cuh"
+#include "ishi_rowstream.cuh"
+
+namespace ishi {
+
+struct FragLaunch {
+  int clusters, split, warps;  // grid = clusters * split CTAs of warps * 32 threads
+  size_t smem;
+  int mode;    // 0: tensor cores, rows 1..8; 1: CUDA cores, one row
+  bool early;  // programmatic dependent launch
+  cudaStream_t stream;
+};
+
+struct FragOps {
+  int tile_bytes, x_bytes;
+  // raises the dynamic shared memory limit of every variant (once per device)
+  cudaError_t (*configure)(int max_smem);
+  // how many clusters of `split` CTAs the device keeps resident, 0 if the launch is impossible
+  int (*max_clusters)(int split, int warps, size_t smem, int sm_count);
+  cudaError_t (*launch)(const FragLaunch &cfg, const FragArgs &args);
+  // the one-time re-tiling into fragment order
+  cudaError_t (*prepare)(const FragSrc &src, int units, uint8_t *dst, int grid, cudaStream_t stream);
+};
+
+struct RowOps {
+  int table_bytes;
+  cudaError_t (*configure)(int max_smem);
+  cudaError_t (*launch)(int rows, int grid, size_t smem, const RowArgs &args, cudaStream_t stream);
+};
+
+}  // namespace ishi

@@ -71,6 +71,39 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
       : "memory");
 }
 
+// the same on shared-memory addresses (32-bit, shared::cta window)
+__device__ __forceinline__ void mbar_init_u32(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_u32(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s_u32(uint32_t dst, const void *src_gmem, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src_gmem), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+  if (mbar_try_wait_u32(bar, parity)) return true;
+  for (uint32_t i = 0; i < kWaitSpins; ++i) {
+    if (mbar_try_wait_u32(bar, parity)) return true;
+    if (*abort_word != 0) return false;
+  }
+  *abort_word = 1;
+  return false;
+}
+
 // ---- shared memory loads ----------------------------------------------------------------------
 // The weight loads are plain (non-volatile) asm so the compiler may interleave them with the
 // tensor-core work of earlier chunks. Ordering against the barriers that guard a stage comes

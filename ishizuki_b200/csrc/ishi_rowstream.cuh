@@ -445,7 +445,7 @@ struct TileSrc {
   int sec_off;           // section offset inside a tile
 };
 
-__global__ void __launch_bounds__(256) prepare_tiles_kernel(TileSrc s0, TileSrc s1, TileSrc s2, TileSrc s3, int nsec,
+static __global__ void __launch_bounds__(256) prepare_tiles_kernel(TileSrc s0, TileSrc s1, TileSrc s2, TileSrc s3, int nsec,
                                                             long long N, int units, int tile_bytes,
                                                             uint8_t *__restrict__ dst) {
   const TileSrc src[4] = {s0, s1, s2, s3};

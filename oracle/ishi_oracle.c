@@ -9,6 +9,9 @@
  *   - oracle_dequant_q6k   Sources/IshizukiKit/Core/GGMLDequant.swift:154-185
  *   - oracle_dequant_iq2xs Sources/IshizukiKit/Core/GGMLDequant.swift:264-285, sign table
  *                          Sources/IshizukiKit/Core/GGMLTables.swift:11-24
+ *   - oracle_dequant_q2k, _iq4xs, _iq2xxs, _iq2s, _iq3xxs, _iq3s, _iq1s, _iq1m
+ *                          Sources/IshizukiKit/Core/GGMLDequant.swift:125-150, 222-262, 287-428,
+ *                          codebooks Sources/IshizukiKit/Core/GGMLTables.swift:26-1137
  *   - oracle_affine_dequant Sources/IshizukiKit/Core/VerifyMatmul.swift:282-287 (code i of a
  *                          row at bit i*bits of the row's word stream, w = float(code)*s + b)
  *                          and Sources/IshizukiKit/Quantize/WeightedAffineQuantizer.swift:142-161
@@ -18,8 +21,9 @@
  *                          compare against (Tests/IshizukiKitTests/GGMLKernelTests.swift:111-140,
  *                          Tests/IshizukiKitTests/VerifyMatmulTests.swift:31-45)
  *
- * Parity pin: the three dequantizers reproduce ggml's own to_float bit for bit on the
- * reference's fixture Tests/IshizukiKitTests/Fixtures/ggml-reference.bin (types 12, 14, 17);
+ * Parity pin: the eleven dequantizers reproduce ggml's own to_float bit for bit on the
+ * reference's fixture Tests/IshizukiKitTests/Fixtures/ggml-reference.bin (types 10, 12, 14,
+ * 16, 17, 18, 19, 21, 22, 23, 29);
  * the rotation reproduces Tests/Golden/hadamard_golden.safetensors case1. The affine formula
  * has no stored vector in the reference (its tests compare against MLX live): that part is
  * pinned by the formula only.
@@ -29,6 +33,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include "../ishizuki_b200/csrc/ggml_tables.h"
 #include "../ishizuki_b200/csrc/iq2xs_tables.h"
 
 /* ---- scalar helpers ---------------------------------------------------------------------- */
@@ -205,23 +210,245 @@ void oracle_dequant_iq2xs(const uint8_t *blocks, int64_t nblocks, float *y) {
   }
 }
 
-/* GGML type ids as in Sources/IshizukiKit/Config/GGUFFile.swift:13-44. */
-enum { GGML_Q4_K = 12, GGML_Q6_K = 14, GGML_IQ2_XS = 17 };
+static uint32_t rd32(const uint8_t *p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+
+static const uint64_t iq2xxs_grid[256] = {ISHI_IQ2_XXS_GRID_LIST};
+static const uint64_t iq2s_grid[1024] = {ISHI_IQ2_S_GRID_LIST};
+static const uint32_t iq3xxs_grid[256] = {ISHI_IQ3_XXS_GRID_LIST};
+static const uint32_t iq3s_grid[512] = {ISHI_IQ3_S_GRID_LIST};
+static const uint64_t iq1s_grid[2048] = {ISHI_IQ1_S_GRID_LIST};
+static const int8_t kvalues_iq4nl[16] = {ISHI_IQ4NL_VALUES_LIST};
+
+static float grid_byte64(uint64_t e, int j) { return (float)((e >> (8 * j)) & 0xff); }
+static float grid_sbyte64(uint64_t e, int j) { return (float)(int8_t)((e >> (8 * j)) & 0xff); }
+static float grid_byte32(uint32_t e, int j) { return (float)((e >> (8 * j)) & 0xff); }
+static float sign_flip(uint8_t signs, int j) { return (signs >> j) & 1 ? -1.0f : 1.0f; }
+
+/* Q2_K, 84 bytes: sixteen (scale | min << 4) bytes @0, 64 bytes of 2-bit codes @16, d f16 @80,
+ * dmin f16 @82. Reference: GGMLDequant.swift:125-150. */
+void oracle_dequant_q2k(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 84;
+    const float d = half_to_float(rd16(p + 80)), dmin = half_to_float(rd16(p + 82));
+    float *out = y + b * 256;
+    int scale = 0;
+    for (int n = 0; n < 256; n += 128) {
+      const uint8_t *q = p + 16 + n / 4;
+      for (int shift = 0; shift < 8; shift += 2) {
+        for (int lane = 0; lane < 2; ++lane) {
+          const uint8_t sc = p[scale++];
+          const float dl = d * (float)(sc & 0xf), ml = dmin * (float)(sc >> 4);
+          for (int l = 0; l < 16; ++l) *out++ = dl * (float)((q[16 * lane + l] >> shift) & 3) - ml;
+        }
+      }
+    }
+  }
+}
+
+/* IQ4_XS, 136 bytes: d f16 @0, scales_h u16 @2, four scales_l bytes @4, 128 nibble bytes @8;
+ * values through the sixteen-entry non-linear table. Reference: GGMLDequant.swift:222-241. */
+void oracle_dequant_iq4xs(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 136;
+    const float d = half_to_float(rd16(p));
+    const uint16_t scales_h = rd16(p + 2);
+    float *out = y + b * 256;
+    for (int ib = 0; ib < 8; ++ib) {
+      const int low = (p[4 + ib / 2] >> (4 * (ib % 2))) & 0xf;
+      const int high = ((scales_h >> (2 * ib)) & 3) << 4;
+      const float dl = d * (float)((low | high) - 32);
+      const uint8_t *qs = p + 8 + 16 * ib;
+      for (int j = 0; j < 16; ++j) {
+        out[j] = dl * (float)kvalues_iq4nl[qs[j] & 0xf];
+        out[16 + j] = dl * (float)kvalues_iq4nl[qs[j] >> 4];
+      }
+      out += 32;
+    }
+  }
+}
+
+/* IQ2_XXS, 66 bytes: d f16 @0, per 32 weights two u32 @2: four grid indices, then four 7-bit
+ * sign indices and a 4-bit scale. Reference: GGMLDequant.swift:243-262. */
+void oracle_dequant_iq2xxs(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 66;
+    const float d = half_to_float(rd16(p));
+    float *out = y + b * 256;
+    for (int ib = 0; ib < 8; ++ib) {
+      const uint32_t aux1 = rd32(p + 2 + 8 * ib), aux2 = rd32(p + 6 + 8 * ib);
+      const float db = d * (0.5f + (float)(aux2 >> 28)) * 0.25f;
+      for (int l = 0; l < 4; ++l) {
+        const uint64_t e = iq2xxs_grid[(aux1 >> (8 * l)) & 0xff];
+        const uint8_t signs = ksigns((aux2 >> (7 * l)) & 127);
+        for (int j = 0; j < 8; ++j) out[j] = db * grid_byte64(e, j) * sign_flip(signs, j);
+        out += 8;
+      }
+    }
+  }
+}
+
+/* IQ2_S, 82 bytes: d f16 @0, 32 index bytes @2, 32 sign bytes @34, 8 qh bytes @66, 8 scale
+ * bytes @74. Reference: GGMLDequant.swift:287-311. */
+void oracle_dequant_iq2s(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 82;
+    const float d = half_to_float(rd16(p));
+    float *out = y + b * 256;
+    for (int ib = 0; ib < 8; ++ib) {
+      const uint8_t scale = p[74 + ib];
+      const float db[2] = {d * (0.5f + (float)(scale & 0xf)) * 0.25f, d * (0.5f + (float)(scale >> 4)) * 0.25f};
+      const int qh = p[66 + ib];
+      for (int l = 0; l < 4; ++l) {
+        const int low = p[2 + 4 * ib + l];
+        const int high = (qh << (8 - 2 * l)) & 0x300;
+        const uint64_t e = iq2s_grid[low | high];
+        const uint8_t signs = p[34 + 4 * ib + l];
+        for (int j = 0; j < 8; ++j) out[j] = db[l / 2] * grid_byte64(e, j) * sign_flip(signs, j);
+        out += 8;
+      }
+    }
+  }
+}
+
+/* IQ3_XXS, 98 bytes: d f16 @0, 64 index bytes @2, per 32 weights one u32 @66 (four 7-bit sign
+ * indices and a 4-bit scale). Reference: GGMLDequant.swift:313-335. */
+void oracle_dequant_iq3xxs(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 98;
+    const float d = half_to_float(rd16(p));
+    float *out = y + b * 256;
+    for (int ib = 0; ib < 8; ++ib) {
+      const uint32_t aux = rd32(p + 66 + 4 * ib);
+      const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+      for (int l = 0; l < 4; ++l) {
+        const uint8_t signs = ksigns((aux >> (7 * l)) & 127);
+        const uint32_t g1 = iq3xxs_grid[p[2 + 8 * ib + 2 * l]], g2 = iq3xxs_grid[p[2 + 8 * ib + 2 * l + 1]];
+        for (int j = 0; j < 4; ++j) {
+          out[j] = db * grid_byte32(g1, j) * sign_flip(signs, j);
+          out[4 + j] = db * grid_byte32(g2, j) * sign_flip(signs, j + 4);
+        }
+        out += 8;
+      }
+    }
+  }
+}
+
+/* IQ3_S, 110 bytes: d f16 @0, 64 index bytes @2, 8 qh bytes @66, 32 sign bytes @74, 4 scale
+ * bytes @106. Reference: GGMLDequant.swift:337-374. */
+void oracle_dequant_iq3s(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 110;
+    const float d = half_to_float(rd16(p));
+    float *out = y + b * 256;
+    for (int pair = 0; pair < 8; pair += 2) {
+      const uint8_t scale = p[106 + pair / 2];
+      const float db[2] = {d * (float)(1 + 2 * (scale & 0xf)), d * (float)(1 + 2 * (scale >> 4))};
+      for (int group = 0; group < 2; ++group) {
+        const int qh = p[66 + pair + group];
+        const uint8_t *qs = p + 2 + 8 * (pair + group);
+        const uint8_t *signs = p + 74 + 4 * (pair + group);
+        for (int l = 0; l < 4; ++l) {
+          const uint32_t g1 = iq3s_grid[qs[2 * l] | ((qh << (8 - 2 * l)) & 256)];
+          const uint32_t g2 = iq3s_grid[qs[2 * l + 1] | ((qh << (7 - 2 * l)) & 256)];
+          for (int j = 0; j < 4; ++j) {
+            out[j] = db[group] * grid_byte32(g1, j) * sign_flip(signs[l], j);
+            out[4 + j] = db[group] * grid_byte32(g2, j) * sign_flip(signs[l], j + 4);
+          }
+          out += 8;
+        }
+      }
+    }
+  }
+}
+
+/* IQ1_S, 50 bytes: d f16 @0, 32 index bytes @2, eight u16 @34 (four 3-bit index extensions, a
+ * 3-bit scale, a delta sign). Reference: GGMLDequant.swift:376-395. */
+void oracle_dequant_iq1s(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 50;
+    const float d = half_to_float(rd16(p));
+    float *out = y + b * 256;
+    for (int ib = 0; ib < 8; ++ib) {
+      const uint16_t qh = rd16(p + 34 + 2 * ib);
+      const float dl = d * (float)(2 * ((qh >> 12) & 7) + 1);
+      const float delta = (qh & 0x8000) ? -0.125f : 0.125f;
+      for (int l = 0; l < 4; ++l) {
+        const uint64_t e = iq1s_grid[p[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)];
+        for (int j = 0; j < 8; ++j) out[j] = dl * (grid_sbyte64(e, j) + delta);
+        out += 8;
+      }
+    }
+  }
+}
+
+/* IQ1_M, 56 bytes: 32 index bytes @0, 16 qh bytes @32, four u16 @48 whose top nibbles spell the
+ * fp16 block scale and whose low 12 bits hold four 3-bit scales. Reference:
+ * GGMLDequant.swift:397-428. */
+void oracle_dequant_iq1m(const uint8_t *blocks, int64_t nblocks, float *y) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    const uint8_t *p = blocks + b * 56;
+    uint16_t sc[4];
+    for (int i = 0; i < 4; ++i) sc[i] = rd16(p + 48 + 2 * i);
+    const uint16_t packed = (uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0) | ((sc[2] >> 4) & 0x0f00) | (sc[3] & 0xf000));
+    const float d = half_to_float(packed);
+    float *out = y + b * 256;
+    for (int ib = 0; ib < 8; ++ib) {
+      const uint16_t word = sc[ib / 2];
+      const int shift = 6 * (ib % 2);
+      const float dl1 = d * (float)(2 * ((word >> shift) & 7) + 1);
+      const float dl2 = d * (float)(2 * ((word >> (shift + 3)) & 7) + 1);
+      const int qh0 = p[32 + 2 * ib], qh1 = p[32 + 2 * ib + 1];
+      const int index[4] = {p[4 * ib] | ((qh0 << 8) & 0x700), p[4 * ib + 1] | ((qh0 << 4) & 0x700),
+                            p[4 * ib + 2] | ((qh1 << 8) & 0x700), p[4 * ib + 3] | ((qh1 << 4) & 0x700)};
+      const float delta[4] = {(qh0 & 0x08) ? -0.125f : 0.125f, (qh0 & 0x80) ? -0.125f : 0.125f,
+                              (qh1 & 0x08) ? -0.125f : 0.125f, (qh1 & 0x80) ? -0.125f : 0.125f};
+      for (int l = 0; l < 4; ++l) {
+        const float dl = l < 2 ? dl1 : dl2;
+        const uint64_t e = iq1s_grid[index[l]];
+        for (int j = 0; j < 8; ++j) out[j] = dl * (grid_sbyte64(e, j) + delta[l]);
+        out += 8;
+      }
+    }
+  }
+}
+
+/* GGML type ids as in Sources/IshizukiKit/Config/GGUFFile.swift:13-44, block sizes as in
+ * :44-80 (pinned by Tests/IshizukiKitTests/GGUFTests.swift:17-35). */
+enum {
+  GGML_Q2_K = 10, GGML_Q4_K = 12, GGML_Q6_K = 14, GGML_IQ2_XXS = 16, GGML_IQ2_XS = 17, GGML_IQ3_XXS = 18,
+  GGML_IQ1_S = 19, GGML_IQ3_S = 21, GGML_IQ2_S = 22, GGML_IQ4_XS = 23, GGML_IQ1_M = 29
+};
 
 int oracle_type_size(int type) {
   switch (type) {
+    case GGML_Q2_K: return 84;
     case GGML_Q4_K: return 144;
     case GGML_Q6_K: return 210;
+    case GGML_IQ2_XXS: return 66;
     case GGML_IQ2_XS: return 74;
+    case GGML_IQ3_XXS: return 98;
+    case GGML_IQ1_S: return 50;
+    case GGML_IQ3_S: return 110;
+    case GGML_IQ2_S: return 82;
+    case GGML_IQ4_XS: return 136;
+    case GGML_IQ1_M: return 56;
     default: return 0;
   }
 }
 
 int oracle_dequant(int type, const uint8_t *blocks, int64_t nblocks, float *y) {
   switch (type) {
+    case GGML_Q2_K: oracle_dequant_q2k(blocks, nblocks, y); return 0;
     case GGML_Q4_K: oracle_dequant_q4k(blocks, nblocks, y); return 0;
     case GGML_Q6_K: oracle_dequant_q6k(blocks, nblocks, y); return 0;
+    case GGML_IQ2_XXS: oracle_dequant_iq2xxs(blocks, nblocks, y); return 0;
     case GGML_IQ2_XS: oracle_dequant_iq2xs(blocks, nblocks, y); return 0;
+    case GGML_IQ3_XXS: oracle_dequant_iq3xxs(blocks, nblocks, y); return 0;
+    case GGML_IQ1_S: oracle_dequant_iq1s(blocks, nblocks, y); return 0;
+    case GGML_IQ3_S: oracle_dequant_iq3s(blocks, nblocks, y); return 0;
+    case GGML_IQ2_S: oracle_dequant_iq2s(blocks, nblocks, y); return 0;
+    case GGML_IQ4_XS: oracle_dequant_iq4xs(blocks, nblocks, y); return 0;
+    case GGML_IQ1_M: oracle_dequant_iq1m(blocks, nblocks, y); return 0;
     default: return -1;
   }
 }

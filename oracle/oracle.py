@@ -15,8 +15,9 @@ import numpy as np
 _HERE = pathlib.Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "libishi_oracle.so"
 
-Q4_K, Q6_K, IQ2_XS = 12, 14, 17
-TYPE_SIZE = {Q4_K: 144, Q6_K: 210, IQ2_XS: 74}
+Q2_K, Q4_K, Q6_K, IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ4_XS, IQ1_M = 10, 12, 14, 16, 17, 18, 19, 21, 22, 23, 29
+TYPE_SIZE = {Q2_K: 84, Q4_K: 144, Q6_K: 210, IQ2_XXS: 66, IQ2_XS: 74, IQ3_XXS: 98, IQ1_S: 50, IQ3_S: 110, IQ2_S: 82,
+             IQ4_XS: 136, IQ1_M: 56}
 SCALE_DTYPE = {np.dtype(np.float16): 0, np.dtype(np.float32): 2}  # bf16 is passed as uint16 + flag
 
 
