@@ -7,8 +7,12 @@
  *
  * Conventions
  *   - Every pointer named *_dev is a device pointer on the context's GPU; the caller owns every
- *     buffer. The library keeps non-owning pointers to weights and owns only its tables and
- *     scratch memory.
+ *     buffer it passes. ishi_projection_create COPIES the weight into the library's own tiled
+ *     layout (same bytes, same compression, another order) and never reads the caller's buffer
+ *     again: the caller may free it after create, and until it does the weight is held twice.
+ *     The kernel-level calls (ishi_ggml_matvec, ishi_ggml_matmul_few, ishi_verify_matmul) take a
+ *     raw weight and re-tile it into the context's scratch on EVERY call (they may reallocate
+ *     that scratch): they exist for tests and tools, a decode loop uses projections.
  *   - Activations are fp16 row-major [M, K]; outputs are fp16 [M, N] with leading dimension
  *     ldy (elements), or [N, M] with leading dimension ldy when ISHI_OUT_TRANSPOSED is set.
  *     Accumulation is fp32.
@@ -41,8 +45,15 @@ enum {
   ISHI_E_TOO_LARGE = 7    /* larger than the built-in scratch of ishi_q4k_matmul_few_static */
 };
 
-/* GGML block types, numbered as in GGUF (Sources/IshizukiKit/Config/GGUFFile.swift:13-44). */
-enum { ISHI_GGML_Q4_K = 12, ISHI_GGML_Q6_K = 14, ISHI_GGML_IQ2_XS = 17 };
+/* GGML block types, numbered as in GGUF (Sources/IshizukiKit/Config/GGUFFile.swift:13-44): the
+ * eleven quantized types the reference reads (GGMLDequant.supported,
+ * Sources/IshizukiKit/Core/GGMLDequant.swift:19-24). Q4_K, Q6_K and IQ2_XS have streaming product
+ * kernels; the others are decoded bit-exactly and multiplied by a one-warp-per-row kernel. */
+enum {
+  ISHI_GGML_Q2_K = 10, ISHI_GGML_Q4_K = 12, ISHI_GGML_Q6_K = 14, ISHI_GGML_IQ2_XXS = 16, ISHI_GGML_IQ2_XS = 17,
+  ISHI_GGML_IQ3_XXS = 18, ISHI_GGML_IQ1_S = 19, ISHI_GGML_IQ3_S = 21, ISHI_GGML_IQ2_S = 22, ISHI_GGML_IQ4_XS = 23,
+  ISHI_GGML_IQ1_M = 29
+};
 
 enum { ISHI_KIND_AFFINE = 0, ISHI_KIND_GGML = 1 };
 enum { ISHI_DT_F16 = 0, ISHI_DT_BF16 = 1, ISHI_DT_F32 = 2 };
@@ -94,9 +105,19 @@ ishi_status ishi_ctx_set_route(ishi_ctx *ctx, int route, int crossover_rows);
 /* ---- projection: PackedLinear ------------------------------------------------------------- */
 
 /* PackedLinear.init + VerifyMatmul.warm (Hadamard.swift:51-86, VerifyMatmul.swift:40-61):
- * validates the weight, fixes the launch plan for its shape and allocates its scratch. */
+ * validates the weight, fixes the launch plan for its shape, allocates the projection's own
+ * memory and copies the weight into it in tiled order (synchronises the device once). */
 ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc,
                                    ishi_projection **out);
+/* Several weights of one format and input width as ONE projection: their output rows stacked in
+ * the order given, y = [x . W0^T | x . W1^T | ...] ([rows, n0 + n1 + ...]). For projections that
+ * read the same input (the reference's q/k/v, Sources/IshizukiKit/Text/Attention.swift:75-83, and
+ * gate/up, Attention.swift:251, which it runs as separate kernels): one launch streams all of them,
+ * so the per-launch costs are paid once. count in 1...4; all descriptors must agree in kind, type,
+ * width, group size, scale dtype, k and rotation. GGUF Q4_K and the 4-/2-bit affine packs only
+ * (ISHI_E_UNSUPPORTED otherwise). */
+ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
+                                         ishi_projection **out);
 void ishi_projection_destroy(ishi_projection *p);
 int64_t ishi_projection_input_dim(const ishi_projection *p);  /* Projection.inputDim */
 int64_t ishi_projection_output_dim(const ishi_projection *p); /* Projection.outputDim */
@@ -117,6 +138,14 @@ ishi_status ishi_projection_rotate(ishi_projection *p, const void *x_dev, int ro
 /* PackedLinear.applyRotated (Hadamard.swift:245-252): multiplies an already rotated input. */
 ishi_status ishi_projection_apply_rotated(ishi_projection *p, const void *xr_dev, int rows,
                                           void *y_dev, int64_t ldy, int flags, void *stream);
+/* The language-model head of a greedy verify step: logits = x . W^T, then per row the index of the
+ * largest logit (fp16 values, the lowest index among equals, as MLX argMax), which is all the
+ * reference's verify loop reads of them (Sources/IshizukiKit/Text/TextModel.swift:350-355,
+ * Sources/IshizukiKit/Generate/SpeculativeGeneration.swift:173-177). argmax_dev: int32 [rows]. The
+ * logits stay in a buffer the projection owns (allocated by the first call: make it outside
+ * stream capture). */
+ishi_status ishi_projection_apply_argmax(ishi_projection *p, const void *x_dev, int rows,
+                                         int32_t *argmax_dev, void *stream);
 /* The same product for a caller whose activations live in host memory: copies x in, multiplies,
  * copies y out, all on the stream; returns once y_host is complete. */
 ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, int rows,
@@ -148,6 +177,12 @@ ishi_status ishi_ggml_matmul_few(ishi_ctx *ctx, const void *x_dev, int rows,
  * ggml's to_float. out_dtype ISHI_DT_F32, ISHI_DT_F16 or ISHI_DT_BF16. */
 ishi_status ishi_ggml_dequantize(ishi_ctx *ctx, int ggml_type, const void *blocks_dev,
                                  int64_t n_blocks, void *out_dev, int out_dtype, void *stream);
+/* GGMLKernels.gather (GGMLKernels.swift:102-138): rows of a quantized table [table_rows, k] by id,
+ * decoded into out [count, k] (the embedding lookup). ids_dev: int32 [count]; an id outside the
+ * table gives a row of zeros. */
+ishi_status ishi_ggml_gather(ishi_ctx *ctx, const int32_t *ids_dev, int64_t count, const void *blocks_dev,
+                             int64_t blocks_bytes, int ggml_type, int64_t table_rows, int64_t k,
+                             void *out_dev, int out_dtype, void *stream);
 /* VerifyMatmul.applyAny (Sources/IshizukiKit/Core/VerifyMatmul.swift:73-120): x [rows, k]
  * against an affine pack. route picks the kernel (ISHI_ROUTE_GEMV or ISHI_ROUTE_MMA). */
 ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x_dev, int rows, const void *w_dev,
@@ -182,16 +217,19 @@ int ishi_ggml_type_size(int ggml_type);
  * of the library image on every GPU that loads it. It calls no cudaMalloc, cudaFree or any other
  * allocating routine.
  *
- * Limits: rows 1...16, k a multiple of 256, at most 131072 output rows, the weight at most
- * 12 MiB of blocks (n * k/256 * 144 bytes, n rounded up to 128), and its partial-sum slots
- * within about 3.9 MiB; anything larger returns ISHI_E_TOO_LARGE and launches nothing.
+ * Limits: rows 1...16, k a multiple of 256, and the weight at most 12 MiB of blocks
+ * (n * k/256 * 144 bytes with n rounded up to a multiple of 128); anything larger returns
+ * ISHI_E_TOO_LARGE and launches nothing. (The array's other parts, arrival counters for 131072
+ * output rows and 3.9 MiB of partial sums, cannot fill up before the weight part does.) A device
+ * that is not sm_100 returns ISHI_E_UNSUPPORTED.
  *
  * The first call on a device looks up the array's device address and sets the kernel's
- * shared-memory limit; make that first call outside any stream capture. The call returns when
- * y is complete. All calls on a device share the one array and it keeps whatever the last call
- * left in it: the counters and the error word are cleared at the start of every call, the rest is
- * overwritten before it is read. Two calls that overlap on the same GPU (two host threads, two
- * streams) race on it: serialise them. */
+ * shared-memory limit. Every call ends by synchronising the stream and reading the error word
+ * back, so it returns when y is complete and it can never be part of a stream capture. All calls
+ * on a device share the one array and it keeps whatever the last call left in it: the counters
+ * and the error word are cleared at the start of every call, the rest is overwritten before it is
+ * read. Two calls that overlap on the same GPU (two host threads, two streams) race on it:
+ * serialise them. */
 ishi_status ishi_q4k_matmul_few_static(const void *x_dev, int rows, const void *blocks_dev,
                                        int64_t blocks_bytes, int64_t n, int64_t k, void *y_dev,
                                        void *stream);
@@ -230,6 +268,11 @@ ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const voi
                                 void *stream);
 /* Enqueues a wait for every rank's latest ishi_exchange_apply to have landed in this rank's buffer. */
 ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream);
+/* Test hook: makes this rank expect `launches_ahead` more launches than were issued, so that the
+ * next ishi_exchange_wait waits for arrival words nobody will write. The wait gives up after its
+ * bound (about a second), raises the context's error word and returns: this is how the
+ * failure path of the bounded waits is exercised without hanging or faulting a GPU. */
+ishi_status ishi_exchange_debug_expect(ishi_exchange *ex, unsigned launches_ahead);
 void ishi_exchange_destroy(ishi_exchange *ex);
 
 #ifdef __cplusplus

@@ -10,6 +10,7 @@ from . import build as _build
 
 OK, E_INVALID, E_SHAPE, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_NOMEM, E_TOO_LARGE = range(8)
 GGML_Q4_K, GGML_Q6_K, GGML_IQ2_XS = 12, 14, 17
+GGML_TYPE_SIZE = {10: 84, 12: 144, 14: 210, 16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 23: 136, 29: 56}
 KIND_AFFINE, KIND_GGML = 0, 1
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 ROUTE_AUTO, ROUTE_GEMV, ROUTE_MMA = 0, 1, 2
@@ -36,12 +37,14 @@ SIGNATURES = {
     "ishi_ctx_poll": (c_int, [c_void_p]),
     "ishi_ctx_set_route": (c_int, [c_void_p, c_int, c_int]),
     "ishi_projection_create": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(c_void_p)]),
+    "ishi_projection_create_fused": (c_int, [c_void_p, POINTER(WeightDesc), c_int, POINTER(c_void_p)]),
     "ishi_projection_destroy": (None, [c_void_p]),
     "ishi_projection_input_dim": (c_int64, [c_void_p]),
     "ishi_projection_output_dim": (c_int64, [c_void_p]),
     "ishi_projection_weight_bytes": (c_int64, [c_void_p]),
     "ishi_projection_crossover_rows": (c_int, [c_void_p]),
     "ishi_projection_apply": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
+    "ishi_projection_apply_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ishi_projection_rotate": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ishi_projection_apply_rotated": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
     "ishi_projection_apply_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
@@ -49,6 +52,7 @@ SIGNATURES = {
     "ishi_ggml_matvec": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "ishi_ggml_matmul_few": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "ishi_ggml_dequantize": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p]),
+    "ishi_ggml_gather": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "ishi_verify_matmul": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "ishi_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "ishi_hadamard_rotate": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
@@ -62,6 +66,7 @@ SIGNATURES = {
     "ishi_exchange_buffer": (c_void_p, [c_void_p]),
     "ishi_exchange_apply": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p]),
     "ishi_exchange_wait": (c_int, [c_void_p, c_void_p]),
+    "ishi_exchange_debug_expect": (c_int, [c_void_p, ctypes.c_uint]),
     "ishi_exchange_destroy": (None, [c_void_p]),
 }
 

@@ -83,6 +83,8 @@ struct ishi_projection {
   int fmt = 0;
   RowPlan plan;          // tcgen05 kernel (formats without a fragment decoder)
   FragPlan frag;         // warp-level kernel
+  bool generic = false;  // neither: the one-warp-per-row kernel reads a plain copy of the blocks (ws.tiles)
+  __half *logits = nullptr;  // [16][n] of apply_argmax, allocated by its first call
   Workspace ws;          // this projection's own scratch and tiled weight: apply never allocates
   __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
   __half *host_x = nullptr, *host_y = nullptr;  // device staging of apply_host_async: [16][k], [16][n]
@@ -107,14 +109,7 @@ ishi_status fail(ishi_ctx *ctx, ishi_status s, const char *fmt, ...) {
     if (e_ != cudaSuccess) return fail(ctx, ISHI_E_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
   } while (0)
 
-int type_size(int t) {
-  switch (t) {
-    case ISHI_GGML_Q4_K: return 144;
-    case ISHI_GGML_Q6_K: return 210;
-    case ISHI_GGML_IQ2_XS: return 74;
-    default: return 0;
-  }
-}
+int type_size(int t) { return ggml_type_size(t); }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -131,6 +126,9 @@ ishi_status check_desc(ishi_ctx *ctx, const ishi_weight_desc &d, int64_t *weight
     if (b < 0 || (b & (b - 1)) != 0 || b > 8192 || d.k % b != 0)
       return fail(ctx, ISHI_E_SHAPE, "Hadamard block %d does not divide input width %lld", b, (long long)d.k);
   }
+  // the product kernel reads the rotation signs four at a time
+  if (d.hadamard_block != 0 && d.signs_dev && !aligned16(d.signs_dev))
+    return fail(ctx, ISHI_E_INVALID, "rotation signs must be 16-byte aligned");
   int64_t bytes = 0, total = 0;
   if (d.kind == ISHI_KIND_GGML) {
     const int ts = type_size(d.ggml_type);
@@ -581,7 +579,16 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
     return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, false, false, st);
   }
   RowPlan pl;
-  if (!make_row_plan(ctx, d, &pl)) return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
+  if (!make_row_plan(ctx, d, &pl)) {
+    if (d.kind == ISHI_KIND_GGML && !row_ops(format_of(d))) {
+      // a block format without a streaming kernel: one warp per output row on the caller's blocks
+      ISHI_CUDA(ctx, launch_ggml_rowdot(d.ggml_type, static_cast<const uint8_t *>(d.weight_dev), d.n, d.k,
+                                        static_cast<const __half *>(x), rows, static_cast<__half *>(y), d.n, 0,
+                                        ctx->sm_count, st));
+      return ISHI_OK;
+    }
+    return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
+  }
   s = ensure_workspace(ctx, &ctx->ws, pl.scratch_floats, pl.counters, pl.tiles_bytes);
   if (s != ISHI_OK) return s;
   s = tile_weight(ctx, pl, d.n, ctx->ws.tiles, st);
@@ -623,6 +630,12 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   if (p->frag.ok)
     return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, ctx->route == ISHI_ROUTE_GEMV,
                     getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, rotate, st);
+  if (p->generic) {
+    if (rotate) return fail(ctx, ISHI_E_INVALID, "in-kernel rotation asked of a kernel that has none");
+    ISHI_CUDA(ctx, launch_ggml_rowdot(p->d.ggml_type, p->ws.tiles, p->d.n, p->d.k, static_cast<const __half *>(x), rows,
+                                      static_cast<__half *>(y), ldy, (flags & ISHI_OUT_TRANSPOSED) ? 1 : 0, ctx->sm_count, st));
+    return ISHI_OK;
+  }
   if (rotate) return fail(ctx, ISHI_E_INVALID, "in-kernel rotation asked of a kernel that has none");
   return run_rows(ctx, p->plan, p->ws, p->fmt, p->d, x, rows, y, ldy, flags, st);
 }
@@ -732,28 +745,29 @@ ishi_status ishi_ggml_dequantize(ishi_ctx *ctx, int type, const void *blocks, in
   if (type_size(type) == 0) return fail(ctx, ISHI_E_UNSUPPORTED, "GGML type %d has no decoder here", type);
   if (n_blocks < 0) return fail(ctx, ISHI_E_SHAPE, "negative block count");
   if (n_blocks == 0) return ISHI_OK;
+  if (out_dtype < ISHI_DT_F16 || out_dtype > ISHI_DT_F32) return fail(ctx, ISHI_E_INVALID, "bad output dtype %d", out_dtype);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int threads = 256;
-  const long long want = (n_blocks * 32 + threads - 1) / threads;
-  const int grid = (int)std::min<long long>(want, (long long)ctx->sm_count * 32);
-  const uint8_t *b = static_cast<const uint8_t *>(blocks);
-#define ISHI_DQ(T, OT) ggml_dequantize_kernel<T, OT><<<grid, threads, 0, st>>>(b, n_blocks, static_cast<OT *>(out))
-#define ISHI_DQ_T(T)                                                             \
-  switch (out_dtype) {                                                           \
-    case ISHI_DT_F32: ISHI_DQ(T, float); break;                                  \
-    case ISHI_DT_F16: ISHI_DQ(T, __half); break;                                 \
-    case ISHI_DT_BF16: ISHI_DQ(T, __nv_bfloat16); break;                         \
-    default: return fail(ctx, ISHI_E_INVALID, "bad output dtype %d", out_dtype); \
-  }
-  switch (type) {
-    case ISHI_GGML_Q4_K: ISHI_DQ_T(12); break;
-    case ISHI_GGML_Q6_K: ISHI_DQ_T(14); break;
-    default: ISHI_DQ_T(17); break;
-  }
-#undef ISHI_DQ_T
-#undef ISHI_DQ
-  ISHI_CUDA(ctx, cudaGetLastError());
+  ISHI_CUDA(ctx, launch_ggml_dequantize(type, static_cast<const uint8_t *>(blocks), n_blocks, out, out_dtype, ctx->sm_count,
+                                        static_cast<cudaStream_t>(stream)));
+  return ISHI_OK;
+}
+
+ishi_status ishi_ggml_gather(ishi_ctx *ctx, const int32_t *ids, int64_t count, const void *blocks, int64_t blocks_bytes,
+                             int type, int64_t table_rows, int64_t k, void *out, int out_dtype, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  if (!ids || !blocks || !out) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  const int ts = type_size(type);
+  if (ts == 0) return fail(ctx, ISHI_E_UNSUPPORTED, "GGML type %d has no decoder here", type);
+  if (out_dtype < ISHI_DT_F16 || out_dtype > ISHI_DT_F32) return fail(ctx, ISHI_E_INVALID, "bad output dtype %d", out_dtype);
+  if (count < 0 || table_rows <= 0 || k <= 0 || k % 256 != 0)
+    return fail(ctx, ISHI_E_SHAPE, "input width %lld is not a whole number of blocks", (long long)k);
+  if (blocks_bytes < table_rows * (k / 256) * ts)
+    return fail(ctx, ISHI_E_SHAPE, "table buffer holds %lld bytes, shape needs %lld", (long long)blocks_bytes,
+                (long long)(table_rows * (k / 256) * ts));
+  if (count == 0) return ISHI_OK;
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ISHI_CUDA(ctx, launch_ggml_gather(type, ids, count, static_cast<const uint8_t *>(blocks), table_rows, k, out, out_dtype,
+                                    ctx->sm_count, static_cast<cudaStream_t>(stream)));
   return ISHI_OK;
 }
 
@@ -829,33 +843,55 @@ ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x, int rows, const voi
 
 // ---- projection: the PackedLinear counterpart ---------------------------------------------------
 
-ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, ishi_projection **out) {
+ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
+                                         ishi_projection **out) {
   if (!ctx || !out) return ISHI_E_INVALID;
   *out = nullptr;
-  if (!desc) return fail(ctx, ISHI_E_INVALID, "null descriptor");
-  int64_t wb = 0;
-  ishi_status s = check_desc(ctx, *desc, &wb);
-  if (s != ISHI_OK) return s;
+  if (!descs) return fail(ctx, ISHI_E_INVALID, "null descriptor");
+  if (count < 1 || count > kFragMaxSegments)
+    return fail(ctx, ISHI_E_SHAPE, "%d weights in one projection, 1...%d are possible", count, kFragMaxSegments);
+  int64_t wb = 0, n_total = 0;
+  for (int i = 0; i < count; ++i) {
+    int64_t part = 0;
+    ishi_status s = check_desc(ctx, descs[i], &part);
+    if (s != ISHI_OK) return s;
+    const ishi_weight_desc &a = descs[0], &b = descs[i];
+    if (a.kind != b.kind || a.ggml_type != b.ggml_type || a.bits != b.bits || a.group_size != b.group_size ||
+        a.scale_dtype != b.scale_dtype || a.hadamard_block != b.hadamard_block || a.k != b.k || a.signs_dev != b.signs_dev)
+      return fail(ctx, ISHI_E_SHAPE, "weight %d differs from weight 0 in format, input width or rotation", i);
+    wb += part;
+    n_total += b.n;
+  }
   std::lock_guard<std::mutex> g(ctx->lock);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   ishi_projection *p = new (std::nothrow) ishi_projection();
   if (!p) return fail(ctx, ISHI_E_NOMEM, "out of host memory");
   p->ctx = ctx;
-  p->d = *desc;
-  p->fmt = format_of(*desc);
+  p->d = descs[0];
+  p->d.n = n_total;  // the projection's output rows: the weights stacked in the order given
+  p->fmt = format_of(descs[0]);
   p->weight_bytes = wb;
-  // Re-tile the weight once, for the kernel this format runs on; the caller's buffer is not read
+  ishi_status s = ISHI_OK;
+  // Re-tile the weight once, for the kernel this format runs on; the caller's buffers are not read
   // again afterwards.
   if (make_frag_plan(ctx, p->d, &p->frag)) {
     s = ensure_workspace(ctx, &p->ws, 0, 0, p->frag.tiles_bytes);
-    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, &p->d, 1, p->d.n, p->ws.tiles, 0);
-  } else {
-    if (!make_row_plan(ctx, p->d, &p->plan)) {
-      delete p;
-      return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)desc->k);
-    }
+    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, descs, count, n_total, p->ws.tiles, 0);
+  } else if (count > 1) {
+    delete p;
+    return fail(ctx, ISHI_E_UNSUPPORTED, "only the warp-level kernel's formats can be stacked into one projection");
+  } else if (make_row_plan(ctx, p->d, &p->plan)) {
     s = ensure_workspace(ctx, &p->ws, p->plan.scratch_floats, p->plan.counters, p->plan.tiles_bytes);
     if (s == ISHI_OK) s = tile_weight(ctx, p->plan, p->d.n, p->ws.tiles, 0);
+  } else if (p->d.kind == ISHI_KIND_GGML && !row_ops(p->fmt)) {
+    // a block format without a streaming kernel: keep a plain copy of the blocks
+    p->generic = true;
+    s = ensure_workspace(ctx, &p->ws, 0, 0, (size_t)wb);
+    if (s == ISHI_OK && cudaMemcpyAsync(p->ws.tiles, descs[0].weight_dev, (size_t)wb, cudaMemcpyDeviceToDevice, 0) != cudaSuccess)
+      s = fail(ctx, ISHI_E_CUDA, "copying the blocks failed");
+  } else {
+    delete p;
+    return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory for k %lld", (long long)descs[0].k);
   }
   if (s == ISHI_OK) {
     cudaError_t e = cudaDeviceSynchronize();
@@ -865,6 +901,8 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
     cudaError_t e = cudaMalloc(&p->xr, (size_t)16 * p->d.k * sizeof(__half));
     if (e != cudaSuccess) s = fail(ctx, ISHI_E_CUDA, "cudaMalloc(rotated x): %s", cudaGetErrorString(e));
   }
+  // after create the library reads only its own tiled copy
+  p->d.weight_dev = p->d.scales_dev = p->d.biases_dev = nullptr;
   if (s != ISHI_OK) {
     free_workspace(&p->ws);
     if (p->xr) cudaFree(p->xr);
@@ -875,6 +913,10 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, 
   return ISHI_OK;
 }
 
+ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, ishi_projection **out) {
+  return ishi_projection_create_fused(ctx, desc, 1, out);
+}
+
 void ishi_projection_destroy(ishi_projection *p) {
   if (!p) return;
   cudaSetDevice(p->ctx->device);
@@ -882,6 +924,7 @@ void ishi_projection_destroy(ishi_projection *p) {
   if (p->xr) cudaFree(p->xr);
   if (p->host_x) cudaFree(p->host_x);
   if (p->host_y) cudaFree(p->host_y);
+  if (p->logits) cudaFree(p->logits);
   delete p;
 }
 
@@ -924,6 +967,27 @@ ishi_status ishi_projection_apply(ishi_projection *p, const void *x, int rows, v
   ishi_status s = ishi_projection_rotate(p, x, rows, p->xr, stream);
   if (s != ISHI_OK) return s;
   return projection_matmul(p, p->xr, rows, y, ldy, flags, false, static_cast<cudaStream_t>(stream));
+}
+
+ishi_status ishi_projection_apply_argmax(ishi_projection *p, const void *x, int rows, int32_t *argmax_dev, void *stream) {
+  if (!p) return ISHI_E_INVALID;
+  ishi_ctx *ctx = p->ctx;
+  if (!x || !argmax_dev) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!p->logits) {
+    // the first call allocates the projection's logits buffer (make it outside stream capture)
+    std::lock_guard<std::mutex> g(ctx->lock);
+    if (!p->logits) {
+      __half *l = nullptr;
+      if (cudaMalloc(&l, (size_t)16 * p->d.n * sizeof(__half)) != cudaSuccess) return fail(ctx, ISHI_E_NOMEM, "logits buffer");
+      p->logits = l;
+    }
+  }
+  ishi_status s = ishi_projection_apply(p, x, rows, p->logits, p->d.n, 0, stream);
+  if (s != ISHI_OK) return s;
+  ISHI_CUDA(ctx, launch_argmax_rows(p->logits, rows, p->d.n, p->d.n, argmax_dev, static_cast<cudaStream_t>(stream)));
+  return ISHI_OK;
 }
 
 ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_host, int rows, void *y_host,
@@ -1123,6 +1187,17 @@ ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream) {
   return ISHI_OK;
 }
 
+ishi_status ishi_exchange_debug_expect(ishi_exchange *ex, unsigned launches_ahead) {
+  if (!ex) return ISHI_E_INVALID;
+  ishi_ctx *ctx = ex->ctx;
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  unsigned seq = 0;
+  ISHI_CUDA(ctx, cudaMemcpy(&seq, ex->words + 17, sizeof(seq), cudaMemcpyDeviceToHost));
+  seq += launches_ahead;
+  ISHI_CUDA(ctx, cudaMemcpy(ex->words + 17, &seq, sizeof(seq), cudaMemcpyHostToDevice));
+  return ISHI_OK;
+}
+
 void ishi_exchange_destroy(ishi_exchange *ex) {
   if (!ex) return;
   cudaSetDevice(ex->ctx->device);
@@ -1165,9 +1240,12 @@ extern "C" ishi_status ishi_q4k_matmul_few_static(const void *x, int rows, const
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ISHI_E_CUDA;
   tmp.device = dev;
+  int major = 0;
   if (cudaDeviceGetAttribute(&tmp.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-      cudaDeviceGetAttribute(&tmp.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+      cudaDeviceGetAttribute(&tmp.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
     return ISHI_E_CUDA;
+  if (major != 10) return ISHI_E_UNSUPPORTED;  // the kernels are built for sm_100a only
 
   ishi_status s = check_io(&tmp, x, rows, y, 16);
   if (s != ISHI_OK) return s;

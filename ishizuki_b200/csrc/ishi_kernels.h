@@ -36,4 +36,15 @@ struct RowOps {
   cudaError_t (*launch)(int rows, int grid, size_t smem, const RowArgs &args, cudaStream_t stream);
 };
 
+// ---- every GGML block format through the shared decoders (ggml_generic.cu) -----------------------
+// out_dtype: 0 fp16, 1 bf16, 2 fp32
+int ggml_type_size(int type);  // bytes of a 256-weight block, 0 for a type without a decoder
+cudaError_t launch_ggml_dequantize(int type, const uint8_t *blocks, long long n_blocks, void *out, int out_dtype, int sm_count,
+                                   cudaStream_t st);
+cudaError_t launch_ggml_gather(int type, const int *ids, long long count, const uint8_t *blocks, long long table_rows,
+                               long long k, void *out, int out_dtype, int sm_count, cudaStream_t st);
+cudaError_t launch_ggml_rowdot(int type, const uint8_t *blocks, long long n, long long k, const __half *x, int rows, __half *y,
+                               long long ldy, int transposed, int sm_count, cudaStream_t st);
+cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, cudaStream_t st);
+
 }  // namespace ishi

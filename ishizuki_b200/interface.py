@@ -38,11 +38,20 @@ def _status_name(status: int) -> str:
 
 
 class GGMLType(enum.IntEnum):
-    """GGUF tensor types this library decodes, numbered as in the file format."""
+    """GGUF tensor types this library decodes, numbered as in the file format (the quantized
+    members of the reference's GGMLDequant.supported)."""
 
+    q2K = 10
     q4K = 12
     q6K = 14
+    iq2Xxs = 16
     iq2Xs = 17
+    iq3Xxs = 18
+    iq1S = 19
+    iq3S = 21
+    iq2S = 22
+    iq4Xs = 23
+    iq1M = 29
 
     @property
     def blockSize(self) -> int:  # noqa: N802 (reference spelling)
@@ -50,7 +59,7 @@ class GGMLType(enum.IntEnum):
 
     @property
     def typeSize(self) -> int:  # noqa: N802
-        return {12: 144, 14: 210, 17: 74}[int(self)]
+        return _lib.GGML_TYPE_SIZE[int(self)]
 
     @property
     def isQuantized(self) -> bool:  # noqa: N802
@@ -180,6 +189,24 @@ class GGMLKernels:
         return out.reshape(tuple(shape))
 
     @staticmethod
+    def gather(ids: torch.Tensor, blocks: torch.Tensor, type: GGMLType, inputDim: int, dtype=torch.bfloat16):  # noqa: N803
+        """The rows named by ids, decoded into [ids.numel(), inputDim] (the embedding lookup)."""
+        try:
+            type = GGMLType(type)
+        except ValueError:
+            return None
+        if inputDim % type.blockSize != 0 or ids.numel() == 0:
+            return None
+        ctx = Context.get(blocks.device.index)
+        idx = ids.reshape(-1).to(torch.int32).contiguous()
+        per_row = inputDim // type.blockSize * type.typeSize
+        table_rows = blocks.numel() // per_row
+        out = torch.empty((idx.numel(), inputDim), dtype=dtype, device=blocks.device)
+        rc = ctx.lib.ishi_ggml_gather(ctx.handle, _ptr(idx), idx.numel(), _ptr(blocks), blocks.numel(), int(type),
+                                      table_rows, inputDim, _ptr(out), _OUT_DT[dtype], _stream())
+        return out if ctx.check(rc, declined=(_lib.E_SHAPE, _lib.E_UNSUPPORTED)) else None
+
+    @staticmethod
     def _product(fn_name: str, x, blocks, type, outputDim):
         x = _as_half_rows(x)
         if x is None:
@@ -266,23 +293,27 @@ class PackedLinear:
         if block > 0 and self.inputDim % block != 0:
             raise ValueError(f"Hadamard block {block} does not divide input width {self.inputDim}")
         self.ctx = Context.get(self.weight.device.index)
-        d = _lib.WeightDesc()
-        d.kind = _lib.KIND_GGML if ggml is not None else _lib.KIND_AFFINE
-        d.ggml_type = int(ggml.type) if ggml is not None else 0
-        d.bits, d.group_size = self.bits, self.groupSize
-        d.scale_dtype = _SCALE_DT[self.scales.dtype] if self.scales is not None else 0
-        d.hadamard_block = block
-        d.n, d.k = self.outputDim, self.inputDim
-        d.weight_dev = self.weight.data_ptr()
-        d.weight_bytes = self.weight.numel() * self.weight.element_size()
-        d.scales_dev = 0 if self.scales is None else self.scales.data_ptr()
-        d.biases_dev = 0 if self.biases is None else self.biases.data_ptr()
-        d.signs_dev = 0 if signs is None else signs.data_ptr()
+        d = self._describe(self.weight, self.scales, self.biases, self.outputDim)
         handle = ctypes.c_void_p()
         rc = self.ctx.lib.ishi_projection_create(self.ctx.handle, ctypes.byref(d), ctypes.byref(handle))
         if rc != _lib.OK:
             raise IshizukiError(rc, self.ctx.last_error())
         self.handle = handle
+
+    def _describe(self, weight, scales, biases, n) -> "_lib.WeightDesc":
+        d = _lib.WeightDesc()
+        d.kind = _lib.KIND_GGML if self.ggml is not None else _lib.KIND_AFFINE
+        d.ggml_type = int(self.ggml.type) if self.ggml is not None else 0
+        d.bits, d.group_size = self.bits, self.groupSize
+        d.scale_dtype = _SCALE_DT[scales.dtype] if scales is not None else 0
+        d.hadamard_block = self.block
+        d.n, d.k = n, self.inputDim
+        d.weight_dev = weight.data_ptr()
+        d.weight_bytes = weight.numel() * weight.element_size()
+        d.scales_dev = 0 if scales is None else scales.data_ptr()
+        d.biases_dev = 0 if biases is None else biases.data_ptr()
+        d.signs_dev = 0 if self.signs is None else self.signs.data_ptr()
+        return d
 
     def __del__(self):
         handle = getattr(self, "handle", None)
@@ -321,6 +352,16 @@ class PackedLinear:
             raise IshizukiError(rc, self.ctx.last_error())
         return y if transposed or out is not None else y.reshape(shape[:-1] + (self.outputDim,))
 
+    def argmax(self, x: torch.Tensor) -> torch.Tensor:
+        """Per row of x the index of its largest logit (int32): the head of a greedy verify step."""
+        self.ctx.sync_route()
+        h, _ = self._rows(x)
+        out = torch.empty(h.shape[0], dtype=torch.int32, device=h.device)
+        rc = self.ctx.lib.ishi_projection_apply_argmax(self.handle, _ptr(h), h.shape[0], _ptr(out), _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+        return out
+
     def rotate(self, x: torch.Tensor) -> torch.Tensor:
         h, shape = self._rows(x)
         xr = torch.empty_like(h)
@@ -355,6 +396,49 @@ class PackedLinear:
                                                            _stream())
         if rc != _lib.OK:
             raise IshizukiError(rc, self.ctx.last_error())
+
+
+class FusedLinear(PackedLinear):
+    """Several projections that read the same input, as one: y = [x . W0^T | x . W1^T | ...].
+
+    The reference runs q / k / v (Sources/IshizukiKit/Text/Attention.swift:75-83) and gate / up
+    (Attention.swift:251) as separate kernels on the same input; here their weights are stacked
+    along the output rows at create time and one launch streams them all. ``parts`` is a list of
+    GGUFBlocks (same type and input width) or of (weight, scales, biases) affine packs (same
+    width, group size and scale dtype). ``split(y)`` gives the parts' outputs back as views."""
+
+    def __init__(self, parts, signs=None, block: int = 0, groupSize: int = 128, bits: int = 2):  # noqa: N803
+        first = parts[0]
+        self.signs, self.block = signs, block
+        if isinstance(first, GGUFBlocks):
+            self.ggml = first
+            self.groupSize, self.bits = first.type.blockSize, 0
+            self.inputDim = first.inputDim
+            self.outputDims = [p.outputDim for p in parts]
+            triples = [(p.bytes, None, None) for p in parts]
+            if any(p.type != first.type or p.inputDim != first.inputDim for p in parts):
+                raise ValueError("stacked GGUF weights must share type and input width")
+        else:
+            self.ggml = None
+            self.groupSize, self.bits = groupSize, bits
+            self.inputDim = first[1].shape[1] * groupSize
+            self.outputDims = [w.shape[0] for w, _, _ in parts]
+            triples = list(parts)
+        self.weight, self.scales, self.biases = triples[0]
+        self.outputDim = sum(self.outputDims)
+        self.ctx = Context.get(self.weight.device.index)
+        descs = (_lib.WeightDesc * len(triples))()
+        for i, (w, s, b) in enumerate(triples):
+            descs[i] = self._describe(w, s, b, self.outputDims[i])
+        handle = ctypes.c_void_p()
+        rc = self.ctx.lib.ishi_projection_create_fused(self.ctx.handle, descs, len(triples), ctypes.byref(handle))
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+        self.handle = handle
+        self.weight = self.scales = self.biases = None  # the library keeps its own tiled copy
+
+    def split(self, y: torch.Tensor, transposed: bool = False):
+        return torch.split(y, self.outputDims, dim=0 if transposed else -1)
 
 
 def hadamardRotate(x: torch.Tensor, block: int, signs: torch.Tensor | None) -> torch.Tensor:  # noqa: N802

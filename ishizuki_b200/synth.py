@@ -8,8 +8,12 @@ from __future__ import annotations
 
 import numpy as np
 
-Q4_K, Q6_K, IQ2_XS = 12, 14, 17
-TYPE_SIZE = {Q4_K: 144, Q6_K: 210, IQ2_XS: 74}
+Q2_K, Q4_K, Q6_K, IQ2_XXS, IQ2_XS, IQ3_XXS, IQ1_S, IQ3_S, IQ2_S, IQ4_XS, IQ1_M = 10, 12, 14, 16, 17, 18, 19, 21, 22, 23, 29
+TYPE_SIZE = {Q2_K: 84, Q4_K: 144, Q6_K: 210, IQ2_XXS: 66, IQ2_XS: 74, IQ3_XXS: 98, IQ1_S: 50, IQ3_S: 110, IQ2_S: 82,
+             IQ4_XS: 136, IQ1_M: 56}
+# byte offsets of the fp16 block scales of every type but IQ1_M (whose scale is spread over four words)
+_SCALE_AT = {Q2_K: (80, 82), Q4_K: (0, 2), Q6_K: (208,), IQ2_XXS: (0,), IQ2_XS: (0,), IQ3_XXS: (0,), IQ1_S: (0,), IQ3_S: (0,),
+             IQ2_S: (0,), IQ4_XS: (0,)}
 
 
 def _half_bytes(values: np.ndarray) -> np.ndarray:
@@ -43,8 +47,29 @@ def q6k_blocks(rng: np.random.Generator, n: int, k: int, d_scale: float = 1e-4) 
     return out.reshape(-1)
 
 
+def other_blocks(rng: np.random.Generator, type_id: int, n: int, k: int, d_scale: float = 2e-3) -> np.ndarray:
+    """[n][k/256][type size] bytes of any block type: uniform random bytes with the fp16 block
+    scales set to |N(0,1)| * d_scale (for IQ1_M the scale's four nibbles sit on top of its words)."""
+    nb = n * (k // 256)
+    ts = TYPE_SIZE[type_id]
+    out = rng.integers(0, 256, size=(nb, ts), dtype=np.uint8)
+    if type_id == IQ1_M:
+        d = (np.abs(rng.standard_normal(nb)) * d_scale).astype(np.float16).view(np.uint16)
+        words = out[:, 48:56].copy().view("<u2")  # [nb, 4]
+        for i in range(4):
+            words[:, i] = (words[:, i] & 0x0FFF) | (((d >> (4 * i)) & 0xF) << 12).astype(np.uint16)
+        out[:, 48:56] = words.view(np.uint8)
+    else:
+        for at in _SCALE_AT[type_id]:
+            out[:, at:at + 2] = _half_bytes(np.abs(rng.standard_normal(nb)) * d_scale)
+    return out.reshape(-1)
+
+
 def ggml_blocks(rng: np.random.Generator, type_id: int, n: int, k: int) -> np.ndarray:
-    return {Q4_K: q4k_blocks, Q6_K: q6k_blocks, IQ2_XS: iq2xs_blocks}[type_id](rng, n, k)
+    special = {Q4_K: q4k_blocks, Q6_K: q6k_blocks, IQ2_XS: iq2xs_blocks}
+    if type_id in special:
+        return special[type_id](rng, n, k)
+    return other_blocks(rng, type_id, n, k)
 
 
 def lcg_blocks(type_id: int, rows: int, k: int, seed: int) -> np.ndarray:

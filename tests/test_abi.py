@@ -24,6 +24,7 @@ def test_constants_that_need_no_device():
     lib = _lib.load()
     # GGUFTests.blockGeometry (Tests/IshizukiKitTests/GGUFTests.swift:17-35)
     assert [lib.ishi_ggml_type_size(t) for t in (12, 14, 17)] == [144, 210, 74]
+    assert [lib.ishi_ggml_type_size(t) for t in (10, 16, 18, 19, 21, 22, 23, 29)] == [84, 66, 98, 50, 110, 82, 136, 56]
     assert [lib.ishi_ggml_block_size(t) for t in (12, 14, 17, 11)] == [256, 256, 256, 0]
     # VerifyMatmulTests.rowFloor
     assert lib.ishi_reference_minimum_rows(248_320 * 5120 * 2 // 8) == 2

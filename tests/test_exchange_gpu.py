@@ -7,13 +7,15 @@ GPUs a two-process run (one rank per GPU) checks that every rank ends up with th
 import os
 import subprocess
 import sys
+import time
 
 import numpy as np
 import pytest
 import torch
 
 from ishizuki_b200 import synth
-from ishizuki_b200.interface import GGMLType, GGUFBlocks, PackedLinear
+from ishizuki_b200 import _lib
+from ishizuki_b200.interface import GGMLType, GGUFBlocks, IshizukiError, PackedLinear
 from ishizuki_b200.sharding import OutputExchange
 
 pytestmark = pytest.mark.gpu
@@ -69,6 +71,32 @@ def test_single_rank_exchange_in_a_replayed_graph():
         torch.cuda.synchronize()
     lin.ctx.poll()
     assert torch.equal(view, want)
+    ex.close()
+
+
+def test_a_wait_nobody_answers_gives_up_and_reports():
+    """Failure detection without a fault: the rank is made to expect one launch more than was
+    issued, so the wait's arrival word never comes. The kernel must return after its bound, the
+    context must report ISHI_E_TIMEOUT once, and the GPU must stay usable."""
+    rng = np.random.default_rng(1)
+    n, k = 256, 512
+    lin = PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
+    x = dev(synth.activations(rng, 8, k))
+    want = lin(x, transposed=True)
+    ex = OutputExchange(1 << 16)
+    off, view = ex.reserve(n)
+    ex.apply(lin, x, off, 0)
+    assert ex.lib.ishi_exchange_debug_expect(ex.handle, 1) == _lib.OK
+    t0 = time.time()
+    ex.wait()
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 20.0
+    with pytest.raises(IshizukiError) as err:
+        ex.ctx.poll()
+    assert err.value.status == _lib.E_TIMEOUT
+    ex.ctx.poll()  # reported once
+    assert torch.equal(view, want)  # the rows of the launch that did happen are there
+    assert torch.equal(lin(x, transposed=True), want)  # and the context still works
     ex.close()
 
 

@@ -8,13 +8,16 @@ import pytest
 import torch
 
 from ishizuki_b200 import synth
-from ishizuki_b200.interface import GGMLKernels, GGMLType, GGUFBlocks, PackedLinear
+from ishizuki_b200 import _lib
+from ishizuki_b200.interface import BonsaiRuntime, FusedLinear, GGMLKernels, GGMLType, GGUFBlocks, IshizukiError, PackedLinear
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [GGMLType.q4K, GGMLType.q6K, GGMLType.iq2Xs]
-MATMUL_TYPES = [GGMLType.q4K, GGMLType.q6K, GGMLType.iq2Xs]
+TYPES = list(GGMLType)  # all eleven block formats the reference reads
+MATMUL_TYPES = list(GGMLType)
+STREAMED = [GGMLType.q4K, GGMLType.q6K, GGMLType.iq2Xs]  # formats with a streaming product kernel
+OTHERS = [t for t in GGMLType if t not in STREAMED]
 TOL = 2e-3  # max |got - want| / max |want|, fp16 output, fp32 accumulate
 
 
@@ -83,9 +86,9 @@ def test_few_row_product_ragged_tile(type_id, m):
     assert rel_err(gotn[finite], want32[finite]) < TOL
 
 
-@pytest.mark.parametrize("type_id", MATMUL_TYPES)
+@pytest.mark.parametrize("type_id", STREAMED)
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (1024, 5120), (6144, 5120), (5120, 6144)])
-@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("m", [1, 2, 4, 8, 16])
 def test_projection_shapes(type_id, n, k, m):
     rng = np.random.default_rng(n + k + m)
     blocks = synth.ggml_blocks(rng, int(type_id), n, k)
@@ -151,3 +154,133 @@ def test_every_launch_plan_gives_the_same_product(plan, monkeypatch):
         err = float(np.abs(got.astype(np.float64) - want32.astype(np.float64)).max() / np.abs(want32).max())
         assert err < 2e-3, (plan, m, err)
     lin.ctx.poll()
+
+
+@pytest.mark.parametrize("type_id", OTHERS)
+@pytest.mark.parametrize("m", [1, 8, 16])
+def test_projection_of_the_other_block_formats(type_id, m):
+    """The eight formats without a streaming kernel go through one warp per output row."""
+    rng = np.random.default_rng(int(type_id) * 31 + m)
+    n, k = 1000, 5120
+    blocks = synth.ggml_blocks(rng, int(type_id), n, k)
+    x = synth.activations(rng, m, k)
+    raw = dev(blocks)
+    lin = PackedLinear(ggml=GGUFBlocks(raw, type_id, (n, k)))
+    raw.zero_()  # the projection keeps its own copy of the blocks
+    y = lin(dev(x))
+    torch.cuda.synchronize()
+    want32, _ = oracle.ggml_matmul(int(type_id), blocks, x, n)
+    assert rel_err(y.cpu().numpy(), want32) < TOL
+    yt = lin(dev(x), transposed=True)
+    assert torch.equal(yt.t().contiguous(), y)
+
+
+def test_single_row_on_cuda_cores_at_a_projection_shape():
+    """ISHI_ROUTE_GEMV: the CUDA-core variant of the warp-level kernel on the 27B gate shape."""
+    rng = np.random.default_rng(77)
+    n, k = 17408, 5120
+    blocks = synth.q4k_blocks(rng, n, k)
+    x = synth.activations(rng, 1, k)
+    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks), GGMLType.q4K, (n, k)))
+    want32, _ = oracle.ggml_matmul(int(GGMLType.q4K), blocks, x, n)
+    BonsaiRuntime.route = _lib.ROUTE_GEMV
+    try:
+        y = lin(dev(x))
+    finally:
+        BonsaiRuntime.route = _lib.ROUTE_AUTO
+    assert rel_err(y.cpu().numpy(), want32) < TOL
+    assert rel_err(lin(dev(x)).cpu().numpy(), want32) < TOL
+
+
+@pytest.mark.parametrize("sizes", [(6144, 1024, 1024), (17, 40, 64), (1000, 24)])
+def test_stacked_projections_are_one_launch_with_the_same_products(sizes):
+    """ishi_projection_create_fused: q / k / v style weights stacked along the output rows."""
+    rng = np.random.default_rng(sum(sizes))
+    k = 5120 if sizes[0] > 100 else 1024
+    parts = [synth.q4k_blocks(rng, n, k) for n in sizes]
+    fused = FusedLinear([GGUFBlocks(dev(b), GGMLType.q4K, (n, k)) for b, n in zip(parts, sizes)])
+    assert fused.outputDim == sum(sizes)
+    for m in (1, 8, 13):
+        x = synth.activations(rng, m, k)
+        y = fused(dev(x))
+        torch.cuda.synchronize()
+        fused.ctx.poll()
+        for piece, blocks, n in zip(fused.split(y), parts, sizes):
+            want32, _ = oracle.ggml_matmul(int(GGMLType.q4K), blocks, x, n)
+            assert rel_err(piece.cpu().numpy(), want32) < TOL
+
+
+def test_stacked_affine_packs():
+    rng = np.random.default_rng(9)
+    k, sizes = 2048, (256, 100)
+    packs = [synth.affine_pack(rng, n, k, 4, 64, np.float16) for n in sizes]
+    fused = FusedLinear([(dev(w), dev(s), dev(b)) for w, s, b in packs], groupSize=64, bits=4)
+    x = synth.activations(rng, 8, k)
+    y = fused(dev(x))
+    for piece, (w, s, b) in zip(fused.split(y), packs):
+        want32, _ = oracle.affine_matmul(w, s, b, 4, 64, x)
+        assert rel_err(piece.cpu().numpy(), want32) < TOL
+
+
+def test_stacking_guards():
+    rng = np.random.default_rng(2)
+    a = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 512)), GGMLType.q4K, (32, 512))
+    b = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 1024)), GGMLType.q4K, (32, 1024))
+    with pytest.raises(ValueError):
+        FusedLinear([a, b])  # different input widths
+    q6 = [GGUFBlocks(dev(synth.q6k_blocks(rng, 32, 512)), GGMLType.q6K, (32, 512)) for _ in range(2)]
+    with pytest.raises(IshizukiError) as err:
+        FusedLinear(q6)  # no fragment decoder: cannot be stacked
+    assert err.value.status == _lib.E_UNSUPPORTED
+
+
+@pytest.mark.parametrize("type_id", [GGMLType.q4K, GGMLType.q6K, GGMLType.iq4Xs, GGMLType.iq2Xxs])
+def test_gather_decodes_the_requested_rows(type_id):
+    """GGMLKernels.gather: the quantized embedding lookup, bit-exact against the decoder."""
+    rng = np.random.default_rng(int(type_id))
+    rows, k = 300, 1024
+    blocks = synth.ggml_blocks(rng, int(type_id), rows, k)
+    table = oracle.dequantize(int(type_id), blocks).reshape(rows, k)
+    ids = np.array([0, 299, 17, 17, 123, 4], dtype=np.int64)
+    got = GGMLKernels.gather(torch.from_numpy(ids).cuda(), dev(blocks), type_id, k, dtype=torch.float32)
+    assert same_bits(got.cpu().numpy(), table[ids])
+    half = GGMLKernels.gather(torch.from_numpy(ids).cuda(), dev(blocks), type_id, k, dtype=torch.float16)
+    assert np.array_equal(half.cpu().numpy().view(np.uint16), table[ids].astype(np.float16).view(np.uint16))
+    outside = GGMLKernels.gather(torch.tensor([5, rows, -1]).cuda(), dev(blocks), type_id, k, dtype=torch.float32)
+    assert same_bits(outside[0].cpu().numpy(), table[5]) and not outside[1:].any()
+    assert GGMLKernels.gather(torch.tensor([1]).cuda(), dev(blocks), type_id, 100) is None
+
+
+@pytest.mark.parametrize("type_id", [GGMLType.q4K, GGMLType.q6K, GGMLType.iq4Xs])
+@pytest.mark.parametrize("m", [1, 8, 16])
+def test_head_argmax_matches_argmax_of_the_logits(type_id, m):
+    """The verify step's head: index of the largest fp16 logit per row, lowest index among equals."""
+    rng = np.random.default_rng(m + int(type_id))
+    n, k = 20000, 1024  # a vocabulary-like output dimension with a ragged last panel
+    blocks = synth.ggml_blocks(rng, int(type_id), n, k)
+    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks), type_id, (n, k)))
+    x = synth.activations(rng, m, k)
+    got = lin.argmax(dev(x)).cpu().numpy()
+    logits = lin(dev(x)).float().cpu().numpy()
+    assert np.array_equal(got, logits.argmax(axis=1))  # numpy also returns the first of equals
+    want32, _ = oracle.ggml_matmul(int(type_id), blocks, x, n)
+    top = want32.max(axis=1)
+    assert np.all(want32[np.arange(m), got] >= top - 2e-3 * np.abs(want32).max())
+
+
+def test_argmax_ties_take_the_lowest_index():
+    n, k = 4096, 256
+    blocks = np.zeros((n, 144), dtype=np.uint8)  # every weight decodes to zero: all logits equal
+    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks.reshape(-1)), GGMLType.q4K, (n, k)))
+    x = synth.activations(np.random.default_rng(0), 4, k)
+    assert lin.argmax(dev(x)).cpu().tolist() == [0, 0, 0, 0]
+
+
+def test_misaligned_rotation_signs_are_refused_before_anything_runs():
+    rng = np.random.default_rng(4)
+    n, k = 64, 512
+    w, sb, bb = synth.ternary_pack(rng, n, k, 128)
+    signs = torch.ones(k + 1, dtype=torch.float32, device="cuda")
+    with pytest.raises(IshizukiError) as err:
+        PackedLinear(dev(w), dev(sb).view(torch.bfloat16), dev(bb).view(torch.bfloat16), signs[1:], 128, groupSize=128, bits=2)
+    assert err.value.status == _lib.E_INVALID

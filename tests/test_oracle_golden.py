@@ -10,7 +10,10 @@ def _same_bits(got: np.ndarray, want: np.ndarray) -> np.ndarray:
     return (got.view(np.uint32) == want.view(np.uint32)) | (np.isnan(got) & np.isnan(want))
 
 
-@pytest.mark.parametrize("type_id", [oracle.Q4_K, oracle.Q6_K, oracle.IQ2_XS])
+ALL_TYPES = sorted(oracle.TYPE_SIZE)  # the eleven quantized block types of GGMLDequant.supported
+
+
+@pytest.mark.parametrize("type_id", ALL_TYPES)
 def test_dequant_matches_ggml_bit_for_bit(ggml_fixture, type_id):
     # Tests/IshizukiKitTests/GGMLDequantTests.swift:60-85: bit patterns equal, NaN == NaN
     blocks, want = ggml_fixture[type_id]
@@ -22,10 +25,10 @@ def test_dequant_matches_ggml_bit_for_bit(ggml_fixture, type_id):
 def test_fixture_has_the_fourteen_types(ggml_fixture):
     assert sorted(ggml_fixture) == [0, 1, 10, 12, 14, 16, 17, 18, 19, 21, 22, 23, 29, 30]
     for type_id, size in oracle.TYPE_SIZE.items():
-        assert ggml_fixture[type_id][0].size == 8 * size  # GGUFTests.blockGeometry: 144 / 210 / 74
+        assert ggml_fixture[type_id][0].size == 8 * size  # GGUFTests.blockGeometry
 
 
-@pytest.mark.parametrize("type_id", [oracle.Q4_K, oracle.Q6_K, oracle.IQ2_XS])
+@pytest.mark.parametrize("type_id", ALL_TYPES)
 def test_dequant_matches_gguf_py(type_id):
     """ggml's own Python reference on larger seeded inputs (independent cross-check)."""
     gguf = pytest.importorskip("gguf")

@@ -17,6 +17,7 @@ import torch
 
 from ishizuki_b200 import _lib, synth
 from ishizuki_b200.interface import GGMLKernels, GGMLType
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-3
@@ -50,6 +51,9 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(n, k, m):
         torch.cuda.synchronize()
         g, w = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert np.abs(g - w).max() <= TOL * np.abs(w).max()
+        # ... and what the CPU oracle gives (this entry point runs its own decoder)
+        want32, _ = oracle.ggml_matmul(oracle.Q4_K, blocks.cpu().numpy(), x.cpu().numpy(), n)
+        assert np.abs(g - want32).max() <= TOL * np.abs(want32).max()
         results.append(g)
     assert not np.array_equal(results[0], results[1])  # different activations, different answers
 
