@@ -49,6 +49,7 @@ SIGNATURES = {
     "ishi_projection_apply_rotated": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
     "ishi_projection_apply_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ishi_projection_apply_host_async": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "ishi_projection_apply_host_batch": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, POINTER(c_void_p), c_int, c_void_p]),
     "ishi_ggml_matvec": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "ishi_ggml_matmul_few": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "ishi_ggml_dequantize": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p]),

@@ -11,6 +11,7 @@
 #include <mutex>
 #include <tuple>
 #include <new>
+#include <vector>
 
 #include "../../include/ishizuki_cuda.h"
 #include "dequant.cuh"
@@ -73,6 +74,10 @@ struct ishi_ctx {
   void *pin_x = nullptr, *pin_y = nullptr;  // pinned staging for apply_host
   void *dev_x = nullptr, *dev_y = nullptr;
   size_t pin_x_bytes = 0, pin_y_bytes = 0;
+  // apply_host_batch: its two copy streams and the events that order them against the caller's stream
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  std::vector<cudaEvent_t> ev_in, ev_done;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   std::mutex lock;
   char last_error[256] = {0};
 };
@@ -706,6 +711,12 @@ void ishi_ctx_destroy(ishi_ctx *ctx) {
   if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
   if (ctx->dev_x) cudaFree(ctx->dev_x);
   if (ctx->dev_y) cudaFree(ctx->dev_y);
+  for (cudaEvent_t e : ctx->ev_in) cudaEventDestroy(e);
+  for (cudaEvent_t e : ctx->ev_done) cudaEventDestroy(e);
+  if (ctx->ev_begin) cudaEventDestroy(ctx->ev_begin);
+  if (ctx->ev_end) cudaEventDestroy(ctx->ev_end);
+  if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
   delete ctx;
 }
 
@@ -990,6 +1001,8 @@ ishi_status ishi_projection_apply_argmax(ishi_projection *p, const void *x, int 
   return ISHI_OK;
 }
 
+static ishi_status ensure_host_staging(ishi_projection *p);
+
 ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_host, int rows, void *y_host,
                                              void *stream) {
   if (!p) return ISHI_E_INVALID;
@@ -998,26 +1011,88 @@ ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_h
   if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
-  if (!p->host_x) {
+  {
     // the first call allocates this projection's device staging (make it outside stream capture)
-    std::lock_guard<std::mutex> g(ctx->lock);
-    if (!p->host_x) {
-      __half *hx = nullptr, *hy = nullptr;
-      ISHI_CUDA(ctx, cudaMalloc(&hx, (size_t)16 * p->d.k * sizeof(__half)));
-      cudaError_t e = cudaMalloc(&hy, (size_t)16 * p->d.n * sizeof(__half));
-      if (e != cudaSuccess) {
-        cudaFree(hx);
-        return fail(ctx, ISHI_E_NOMEM, "device staging: %s", cudaGetErrorString(e));
-      }
-      p->host_y = hy;
-      p->host_x = hx;
-    }
+    ishi_status s0 = ensure_host_staging(p);
+    if (s0 != ISHI_OK) return s0;
   }
   const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * p->d.n * sizeof(__half);
   ISHI_CUDA(ctx, cudaMemcpyAsync(p->host_x, x_host, xb, cudaMemcpyHostToDevice, st));
   ishi_status s = ishi_projection_apply(p, p->host_x, rows, p->host_y, p->d.n, 0, stream);
   if (s != ISHI_OK) return s;
   ISHI_CUDA(ctx, cudaMemcpyAsync(y_host, p->host_y, yb, cudaMemcpyDeviceToHost, st));
+  return ISHI_OK;
+}
+
+// device staging of the host-buffer entry points: [16][k] and [16][n], allocated by the first call
+static ishi_status ensure_host_staging(ishi_projection *p) {
+  ishi_ctx *ctx = p->ctx;
+  if (p->host_x) return ISHI_OK;
+  std::lock_guard<std::mutex> g(ctx->lock);
+  if (p->host_x) return ISHI_OK;
+  __half *hx = nullptr, *hy = nullptr;
+  ISHI_CUDA(ctx, cudaMalloc(&hx, (size_t)16 * p->d.k * sizeof(__half)));
+  cudaError_t e = cudaMalloc(&hy, (size_t)16 * p->d.n * sizeof(__half));
+  if (e != cudaSuccess) {
+    cudaFree(hx);
+    return fail(ctx, ISHI_E_NOMEM, "device staging: %s", cudaGetErrorString(e));
+  }
+  p->host_y = hy;
+  p->host_x = hx;
+  return ISHI_OK;
+}
+
+ishi_status ishi_projection_apply_host_batch(ishi_projection *const *ps, const void *const *x_hosts, int rows,
+                                             void *const *y_hosts, int count, void *stream) {
+  if (!ps || count < 1 || !ps[0]) return ISHI_E_INVALID;
+  ishi_ctx *ctx = ps[0]->ctx;
+  if (!x_hosts || !y_hosts) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  for (int i = 0; i < count; ++i) {
+    if (!ps[i] || !x_hosts[i] || !y_hosts[i]) return fail(ctx, ISHI_E_INVALID, "null pointer in entry %d", i);
+    if (ps[i]->ctx != ctx) return fail(ctx, ISHI_E_INVALID, "projection %d belongs to another context", i);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  {
+    std::lock_guard<std::mutex> g(ctx->lock);
+    if (!ctx->copy_in) {
+      ISHI_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+      ISHI_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+      ISHI_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_begin, cudaEventDisableTiming));
+      ISHI_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_end, cudaEventDisableTiming));
+    }
+    while ((int)ctx->ev_in.size() < count) {
+      cudaEvent_t a = nullptr, b = nullptr;
+      ISHI_CUDA(ctx, cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+      ctx->ev_in.push_back(a);
+      ISHI_CUDA(ctx, cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+      ctx->ev_done.push_back(b);
+    }
+  }
+  for (int i = 0; i < count; ++i) {
+    ishi_status s = ensure_host_staging(ps[i]);
+    if (s != ISHI_OK) return s;
+  }
+  // Three lanes: x copies run ahead on one stream, the products follow on the caller's stream as
+  // their inputs land, the y copies trail on a third; the caller's stream ends behind all of them.
+  ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_begin, st));
+  ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->ev_begin, 0));
+  ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_begin, 0));
+  for (int i = 0; i < count; ++i) {
+    ishi_projection *p = ps[i];
+    const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * p->d.n * sizeof(__half);
+    ISHI_CUDA(ctx, cudaMemcpyAsync(p->host_x, x_hosts[i], xb, cudaMemcpyHostToDevice, ctx->copy_in));
+    ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_in[i], ctx->copy_in));
+    ISHI_CUDA(ctx, cudaStreamWaitEvent(st, ctx->ev_in[i], 0));
+    ishi_status s = ishi_projection_apply(p, p->host_x, rows, p->host_y, p->d.n, 0, stream);
+    if (s != ISHI_OK) return s;
+    ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_done[i], st));
+    ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[i], 0));
+    ISHI_CUDA(ctx, cudaMemcpyAsync(y_hosts[i], p->host_y, yb, cudaMemcpyDeviceToHost, ctx->copy_out));
+  }
+  ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_end, ctx->copy_out));
+  ISHI_CUDA(ctx, cudaStreamWaitEvent(st, ctx->ev_end, 0));
   return ISHI_OK;
 }
 

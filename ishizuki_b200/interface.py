@@ -398,6 +398,28 @@ class PackedLinear:
             raise IshizukiError(rc, self.ctx.last_error())
 
 
+class HostBatch:
+    """A fixed list of projections with page-locked host inputs and outputs, run by one C call
+    (ishi_projection_apply_host_batch): the copies in, the products and the copies out overlap."""
+
+    def __init__(self, layers, xs, ys):
+        """layers: PackedLinear objects of one context; xs[i] [rows, k_i], ys[i] [rows, n_i]: contiguous
+        fp16 CPU tensors (pinned for the copies to be asynchronous)."""
+        self.layers, self.xs, self.ys = list(layers), list(xs), list(ys)
+        n = len(self.layers)
+        self.rows = self.xs[0].shape[0]
+        self._p = (ctypes.c_void_p * n)(*[lin.handle.value for lin in self.layers])
+        self._x = (ctypes.c_void_p * n)(*[x.data_ptr() for x in self.xs])
+        self._y = (ctypes.c_void_p * n)(*[y.data_ptr() for y in self.ys])
+        self.ctx = self.layers[0].ctx
+
+    def run(self) -> None:
+        """Enqueues the whole list; the outputs are valid once the current stream is synchronised."""
+        rc = self.ctx.lib.ishi_projection_apply_host_batch(self._p, self._x, self.rows, self._y, len(self.layers), _stream())
+        if rc != _lib.OK:
+            raise IshizukiError(rc, self.ctx.last_error())
+
+
 class FusedLinear(PackedLinear):
     """Several projections that read the same input, as one: y = [x . W0^T | x . W1^T | ...].
 

@@ -16,7 +16,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-GGML_TYPE_SIZE = {12: 144, 14: 210, 17: 74}
+GGML_TYPE_SIZE = {10: 84, 12: 144, 14: 210, 16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 23: 136, 29: 56}
 
 
 def row_range(n: int, rank: int, world: int) -> tuple[int, int]:

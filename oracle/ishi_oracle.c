@@ -614,6 +614,18 @@ int oracle_reference_minimum_rows(int64_t bytes) {
   return 6;
 }
 
+/* The threads the products above run on; n > 0 sets it (a launcher may have pinned OMP_NUM_THREADS
+ * to 1 for its workers, which would make a CPU baseline single-threaded by accident). */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+  return 0;
+}
+
 int oracle_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);

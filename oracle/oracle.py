@@ -53,6 +53,8 @@ def _load() -> ctypes.CDLL:
     lib.oracle_reference_minimum_rows.argtypes = [c.c_int64]
     lib.oracle_reference_minimum_rows.restype = c.c_int
     lib.oracle_threads.restype = c.c_int
+    lib.oracle_set_threads.argtypes = [c.c_int]
+    lib.oracle_set_threads.restype = c.c_int
     lib.oracle_float_to_half.argtypes = [c.c_float]
     lib.oracle_float_to_half.restype = c.c_uint16
     return lib
@@ -78,6 +80,15 @@ def _c(a: np.ndarray) -> np.ndarray:
 
 def threads() -> int:
     return int(lib().oracle_threads())
+
+
+def use_all_cores() -> int:
+    """Runs the products on every core this process may use, whatever OMP_NUM_THREADS says."""
+    import os
+
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(n)
+    return threads()
 
 
 def dequantize(type_id: int, blocks: np.ndarray) -> np.ndarray:
