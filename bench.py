@@ -54,6 +54,12 @@ SEED = 1234
 METRIC = "quantized-matmul weight GB/s (% of HBM peak) at M=1/8 draft rows; µs/layer"
 
 
+def log(msg: str) -> None:
+    """Progress lines on stderr (ISHI_BENCH_VERBOSE=1); stdout carries the one JSON line only."""
+    if os.environ.get("ISHI_BENCH_VERBOSE") == "1":
+        print("[bench rank %s] %s" % (os.environ.get("RANK", "0"), msg), file=sys.stderr, flush=True)
+
+
 def weight_bytes(n: int, k: int) -> int:
     return n * (k // 256) * 144
 
@@ -366,6 +372,17 @@ def format_table(peak: float) -> dict:
         table[fmt] = row
         del lins
         torch.cuda.empty_cache()
+    # one row on CUDA cores beside the tensor-core kernel on the smallest and the tallest projection
+    for name, n_, k_ in (("q4_k_kv_1024x5120", 1024, 5120), ("q4_k_down_5120x17408", 5120, 17408)):
+        lins = [make("q4_k", n_, k_) for _ in range(8 if n_ < 2048 else 4)]
+        row = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k_)}
+        BonsaiRuntime.route = _lib.ROUTE_GEMV
+        try:
+            row["m1_cuda_cores"] = measure(lins, 1, k_)
+        finally:
+            BonsaiRuntime.route = _lib.ROUTE_AUTO
+        table[name] = row
+        del lins
     # configuration 1: a single 4096 x 4096 affine 4-bit group-64 projection (32 distinct weights)
     lins = [make("affine4_g64", 4096, 4096) for _ in range(32)]
     table["affine4_g64_4096x4096"] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, 4096),
@@ -417,6 +434,7 @@ def run_ours(args) -> dict | None:
     use_nccl = os.environ.get("ISHI_BENCH_NCCL") == "1"  # N > 1: all-gather per launch instead of the exchange
     exchange = None
     exchange_note = None
+    nccl_group = None
     out_rows_per_layer = sum(sum(n for _, n in mats) for _, _, mats in groups)
     if world > 1 and not use_nccl:
         from ishizuki_b200.sharding import OutputExchange
@@ -435,6 +453,11 @@ def run_ours(args) -> dict | None:
                 exchange.close()
             exchange = None
             exchange_note = exchange_note or "output exchange unavailable on another rank: NCCL all-gather instead"
+
+    if world > 1 and exchange is None:
+        from ishizuki_b200.sharding import NcclGroup
+
+        nccl_group = NcclGroup()  # ishi_group_*: the library's own communicator, NCCL's non-blocking mode
 
     # (projection, x, y_local or exchange offset, y_full view, rows of all ranks, k, row offset, (layer, group, first part, parts))
     launches = []
@@ -456,8 +479,8 @@ def run_ours(args) -> dict | None:
                 if exchange is not None:
                     y_local, y_full = exchange.reserve(n_all)  # (byte offset, [n_all, 8] view of this rank's copy)
                 elif world > 1:
-                    y_local = torch.empty((n_local, ROWS), dtype=torch.float16, device="cuda")
                     y_full = torch.empty((n_all, ROWS), dtype=torch.float16, device="cuda")
+                    y_local = y_full[rank * n_local: (rank + 1) * n_local]  # the product writes its slab in place
                 else:
                     y_local = torch.empty((ROWS, n_local), dtype=torch.float16, device="cuda")
                     y_full = y_local
@@ -467,6 +490,7 @@ def run_ours(args) -> dict | None:
                 total_weight += weight_bytes(n_all, k)
                 total_alg += algorithmic_bytes(n_all, k, ROWS)
     torch.cuda.empty_cache()
+    log("%d launches per step, %.2f GB of weights" % (len(launches), total_weight / 1e9))
 
     def one_pass():
         for lin, x, y_local, y_full, _, _, row0, _ in launches:
@@ -475,8 +499,7 @@ def run_ours(args) -> dict | None:
                 # ranks' previous launch, whose outputs a layer stack's data flow makes it depend on
                 exchange.apply(lin, x, y_local, row0, wait_previous=True)
             elif world > 1:
-                lin(x, transposed=True, out=y_local)
-                dist.all_gather_into_tensor(y_full, y_local)
+                nccl_group.apply(lin, x, y_full)  # ishi_projection_apply_sharded: product + ncclAllGather
             else:
                 lin(x, out=y_local)
         if exchange is not None:
@@ -502,6 +525,7 @@ def run_ours(args) -> dict | None:
             else:
                 one_pass()
 
+        log("first pass done, graph %s" % ("captured" if graph is not None else "not used"))
         for _ in range(args.warmup):
             step()
         torch.cuda.synchronize()
@@ -524,6 +548,7 @@ def run_ours(args) -> dict | None:
             ms = float(t.item())
             dist.barrier()
         ctx.poll()
+        log("timed region done: %.3f ms per step" % (ms / args.steps))
 
         # N > 1, outside the timed region: are the assembled outputs what the ranks computed? Every
         # rank rebuilds every rank's shard of a sample of launches from the seeds, multiplies it
@@ -561,6 +586,7 @@ def run_ours(args) -> dict | None:
                      "ok": bool(flags[0].item() < 2e-3)}
             ctx.poll()
 
+        log("exchange check: %s" % (check,))
         # End to end through the host-buffer entry point: every launch's x comes from page-locked
         # host memory and its y (this rank's rows) goes back to page-locked host memory inside the
         # timed region, one C call and one stream synchronisation per step, after which a value of
@@ -594,6 +620,7 @@ def run_ours(args) -> dict | None:
             "checksum": checksum,
         }
 
+    log("end to end done")
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -619,7 +646,8 @@ def run_ours(args) -> dict | None:
             "stacked": "q+k+v and gate+up are one launch each" if fused else "one launch per matrix",
             "l2": "every projection has its own weights: %.2f GB per step" % (total_weight / 1e9),
             "parallelism": ("N-sharded x%d, outputs exchanged by the product kernels over NVLink" % world if exchange is not None
-                            else "N-sharded x%d + NCCL all-gather" % world) if world > 1 else "single GPU",
+                            else "N-sharded x%d + one NCCL all-gather per launch (ishi_projection_apply_sharded)" % world)
+            if world > 1 else "single GPU",
             "launch": "CUDA graph" if graph is not None else "eager",
         },
         **({"note": exchange_note} if exchange_note else {}),

@@ -42,7 +42,8 @@ enum {
   ISHI_E_CUDA = 4,        /* a CUDA runtime call failed; see ishi_last_error */
   ISHI_E_TIMEOUT = 5,     /* a bounded device-side wait gave up; outputs of that call are invalid */
   ISHI_E_NOMEM = 6,
-  ISHI_E_TOO_LARGE = 7    /* larger than the built-in scratch of ishi_q4k_matmul_few_static */
+  ISHI_E_TOO_LARGE = 7,   /* larger than the built-in scratch of ishi_q4k_matmul_few_static */
+  ISHI_E_NCCL = 8         /* an NCCL call failed or the communicator was aborted; see ishi_group_last_error */
 };
 
 /* GGML block types, numbered as in GGUF (Sources/IshizukiKit/Config/GGUFFile.swift:13-44): the
@@ -98,8 +99,11 @@ const char *ishi_last_error(const ishi_ctx *ctx);
 ishi_status ishi_ctx_poll(ishi_ctx *ctx);
 /* Runtime switches, the counterpart of BonsaiRuntime.useVerifyMatmul and the tunables of
  * VerifyMatmul (Sources/IshizukiKit/Core/RuntimeOptions.swift:43-54,
- * Sources/IshizukiKit/Core/VerifyMatmul.swift:28-33). route: ISHI_ROUTE_*; crossover_rows:
- * rows from which AUTO picks the tensor-core kernel (0 restores the built-in table). */
+ * Sources/IshizukiKit/Core/VerifyMatmul.swift:28-33). route: ISHI_ROUTE_GEMV sends a single row to
+ * the CUDA-core kernel (formats of the warp-level kernel), ISHI_ROUTE_MMA never does, and
+ * ISHI_ROUTE_AUTO does when crossover_rows > 1: crossover_rows is the row count from which AUTO
+ * uses the tensor-core kernel (0 restores the built-in value, 1: the tensor-core kernel measured
+ * faster on B200 at one row on every benchmark shape). */
 ishi_status ishi_ctx_set_route(ishi_ctx *ctx, int route, int crossover_rows);
 
 /* ---- projection: PackedLinear ------------------------------------------------------------- */
@@ -123,8 +127,9 @@ int64_t ishi_projection_input_dim(const ishi_projection *p);  /* Projection.inpu
 int64_t ishi_projection_output_dim(const ishi_projection *p); /* Projection.outputDim */
 /* Compressed weight bytes one apply streams (codes + scales + biases, or GGUF blocks). */
 int64_t ishi_projection_weight_bytes(const ishi_projection *p);
-/* Rows from which this projection's AUTO route uses the tensor-core kernel; the counterpart of
- * VerifyMatmul.minimumRows(bytes:) (VerifyMatmul.swift:19-26), re-measured for B200. */
+/* Rows from which this projection's AUTO route uses the tensor-core kernel: the context's
+ * crossover_rows, or the built-in 1. The counterpart of VerifyMatmul.minimumRows(bytes:)
+ * (VerifyMatmul.swift:19-26), whose table was tuned for Apple M1 (ishi_reference_minimum_rows). */
 int ishi_projection_crossover_rows(const ishi_projection *p);
 
 /* PackedLinear.callAsFunction (Hadamard.swift:180-213): rotates x when the pack is rotated,
@@ -283,6 +288,34 @@ ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream);
  * failure path of the bounded waits is exercised without hanging or faulting a GPU. */
 ishi_status ishi_exchange_debug_expect(ishi_exchange *ex, unsigned launches_ahead);
 void ishi_exchange_destroy(ishi_exchange *ex);
+
+/* ---- N-sharded projections: one NCCL all-gather per projection --------------------------------
+ *
+ * The plain way to assemble an N-sharded projection (no counterpart in the single-GPU reference):
+ * every rank multiplies its rows and one ncclAllGather of the fp16 rows gives every rank the whole
+ * output. A group owns one NCCL communicator in non-blocking mode; NCCL is loaded at run time
+ * (libnccl.so.2), a host without it gets ISHI_E_UNSUPPORTED. Nothing here blocks for ever: a rank
+ * that never arrives ends in ISHI_E_TIMEOUT after timeout_ms and the communicator is aborted. */
+typedef struct ishi_group ishi_group;
+enum { ISHI_GROUP_ID_BYTES = 128 };
+/* Rank 0 calls this (ncclGetUniqueId) and hands the bytes to every rank by any means it has. */
+ishi_status ishi_group_unique_id(void *id_out);
+/* All ranks call this with the same id, on the GPU that is current for the calling thread. A group
+ * is returned even on failure when its message is worth reading (destroy it as usual). */
+ishi_status ishi_group_create(const void *id, int rank, int world, int timeout_ms, ishi_group **out);
+const char *ishi_group_last_error(const ishi_group *g);
+/* x [rows, k] against this rank's shard p (n_local rows, the same on every rank): y_all_dev is
+ * fp16 [world * n_local][rows], rank r's rows at [r * n_local, (r + 1) * n_local), the transposed
+ * form of ishi_projection_apply; the product writes this rank's slab in place and the all-gather
+ * fills the rest, both on the stream. rows in 1...16. */
+ishi_status ishi_projection_apply_sharded(ishi_group *g, ishi_projection *p, const void *x_dev, int rows,
+                                          void *y_all_dev, void *stream);
+void ishi_group_destroy(ishi_group *g);
+/* Test hook: replaces the NCCL entry points the library uses by the table given (seven function
+ * pointers in the order ncclGetUniqueId, ncclCommInitRankConfig, ncclCommGetAsyncError,
+ * ncclAllGather, ncclCommAbort, ncclCommDestroy, ncclGetErrorString), or restores the real ones
+ * with NULL. Lets the error and time-out paths be exercised on a machine without GPUs. */
+ishi_status ishi_group_debug_set_api(const void *table);
 
 #ifdef __cplusplus
 }

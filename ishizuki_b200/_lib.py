@@ -8,7 +8,8 @@ from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 
 from . import build as _build
 
-OK, E_INVALID, E_SHAPE, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_NOMEM, E_TOO_LARGE = range(8)
+OK, E_INVALID, E_SHAPE, E_UNSUPPORTED, E_CUDA, E_TIMEOUT, E_NOMEM, E_TOO_LARGE, E_NCCL = range(9)
+GROUP_ID_BYTES = 128
 GGML_Q4_K, GGML_Q6_K, GGML_IQ2_XS = 12, 14, 17
 GGML_TYPE_SIZE = {10: 84, 12: 144, 14: 210, 16: 66, 17: 74, 18: 98, 19: 50, 21: 110, 22: 82, 23: 136, 29: 56}
 KIND_AFFINE, KIND_GGML = 0, 1
@@ -61,6 +62,12 @@ SIGNATURES = {
     "ishi_ggml_block_size": (c_int, [c_int]),
     "ishi_ggml_type_size": (c_int, [c_int]),
     "ishi_q4k_matmul_few_static": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ishi_group_unique_id": (c_int, [c_void_p]),
+    "ishi_group_create": (c_int, [c_void_p, c_int, c_int, c_int, POINTER(c_void_p)]),
+    "ishi_group_last_error": (c_char_p, [c_void_p]),
+    "ishi_projection_apply_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "ishi_group_destroy": (None, [c_void_p]),
+    "ishi_group_debug_set_api": (c_int, [c_void_p]),
     "ishi_exchange_create": (c_int, [c_void_p, c_int, c_int, c_int64, POINTER(c_void_p)]),
     "ishi_exchange_export": (c_int, [c_void_p, c_void_p]),
     "ishi_exchange_connect": (c_int, [c_void_p, c_void_p]),

@@ -66,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{out}\n{err}")
         if verbose:
             print(err)
-    link = subprocess.run([nvcc, "-shared", "-o", str(LIB), *map(str, objects)], capture_output=True, text=True)
+    link = subprocess.run([nvcc, "-shared", "-o", str(LIB), *map(str, objects), "-ldl"], capture_output=True, text=True)
     if link.returncode != 0:
         raise RuntimeError(f"link failed:\n{link.stdout}\n{link.stderr}")
     return LIB

@@ -499,6 +499,15 @@ struct PeerOut {
   long long row_offset;
 };
 
+// Does a single row go to the CUDA-core kernel? ISHI_ROUTE_GEMV: yes; ISHI_ROUTE_MMA: no; AUTO: when
+// the crossover is above one row. The built-in crossover is 1 (the tensor-core kernel is the faster
+// one on B200 at every row count, measured per shape in the benchmark's side table).
+bool single_row_on_cuda_cores(const ishi_ctx *ctx) {
+  if (ctx->route == ISHI_ROUTE_GEMV) return true;
+  if (ctx->route == ISHI_ROUTE_MMA) return false;
+  return ctx->crossover_rows > 1;
+}
+
 // rows 1...16 through the warp-level kernel; gemv picks the CUDA-core variant for a single row
 ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, const ishi_weight_desc &d, const void *x,
                      int rows, void *y, long long ldy, int flags, bool gemv, bool early, bool rotate, cudaStream_t st,
@@ -581,7 +590,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
     if (s != ISHI_OK) return s;
     s = tile_weight_frag(ctx, fp, &d, 1, d.n, ctx->ws.tiles, st);
     if (s != ISHI_OK) return s;
-    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || ctx->route == ISHI_ROUTE_GEMV, false, false, st);
+    return run_frag(ctx, fp, ctx->ws, d, x, rows, y, d.n, 0, gemv || single_row_on_cuda_cores(ctx), false, false, st);
   }
   RowPlan pl;
   if (!make_row_plan(ctx, d, &pl)) {
@@ -633,7 +642,7 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   if (ldy < need_ld) return fail(ctx, ISHI_E_SHAPE, "ldy %lld shorter than %lld", (long long)ldy, (long long)need_ld);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   if (p->frag.ok)
-    return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, ctx->route == ISHI_ROUTE_GEMV,
+    return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, single_row_on_cuda_cores(ctx),
                     getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, rotate, st);
   if (p->generic) {
     if (rotate) return fail(ctx, ISHI_E_INVALID, "in-kernel rotation asked of a kernel that has none");
@@ -665,6 +674,7 @@ const char *ishi_status_string(ishi_status s) {
     case ISHI_E_TIMEOUT: return "device-side wait timed out";
     case ISHI_E_NOMEM: return "out of memory";
     case ISHI_E_TOO_LARGE: return "larger than the built-in scratch of the no-allocation entry point";
+    case ISHI_E_NCCL: return "NCCL error";
     default: return "unknown status";
   }
 }

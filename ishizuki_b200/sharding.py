@@ -74,6 +74,51 @@ class ShardedLinear:
         return gather_rows(y_local_t, self.n, self.group).t()
 
 
+class NcclGroup:
+    """The NCCL all-gather path of the C ABI (ishi_group_*): one communicator per process, created
+    from an id that rank 0 draws and the host process group passes around."""
+
+    def __init__(self, group=None, timeout_ms: int = 30000):
+        import ctypes
+
+        from . import _lib
+        from .interface import IshizukiError
+
+        self.lib = _lib.load()
+        self._err = IshizukiError
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        blob = ctypes.create_string_buffer(_lib.GROUP_ID_BYTES)
+        if self.rank == 0:
+            rc = self.lib.ishi_group_unique_id(blob)
+            if rc != 0:
+                raise IshizukiError(rc, "ishi_group_unique_id failed")
+        ids = [bytes(blob.raw)]
+        if self.world > 1:
+            dist.broadcast_object_list(ids, src=0, group=group)
+        handle = ctypes.c_void_p()
+        rc = self.lib.ishi_group_create(ctypes.create_string_buffer(ids[0], _lib.GROUP_ID_BYTES), self.rank, self.world,
+                                        timeout_ms, ctypes.byref(handle))
+        self.handle = handle
+        if rc != 0:
+            raise IshizukiError(rc, self.lib.ishi_group_last_error(handle).decode())
+
+    def apply(self, local, x: torch.Tensor, y_all: torch.Tensor) -> None:
+        """local: interface.PackedLinear over this rank's rows; y_all [world * n_local, rows] fp16."""
+        import ctypes
+
+        rc = self.lib.ishi_projection_apply_sharded(self.handle, local.handle, ctypes.c_void_p(x.data_ptr()), x.shape[0],
+                                                    ctypes.c_void_p(y_all.data_ptr()),
+                                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise self._err(rc, self.lib.ishi_group_last_error(self.handle).decode() or local.ctx.last_error())
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.ishi_group_destroy(self.handle)
+            self.handle = None
+
+
 class _DeviceView:
     """A raw device range as something torch.as_tensor accepts (CUDA array interface)."""
 

@@ -101,11 +101,16 @@ def test_a_wait_nobody_answers_gives_up_and_reports():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_exchange_whole_outputs():
-    script = os.path.join(os.path.dirname(__file__), "exchange_two_ranks.py")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29533", script]
+def test_all_ranks_end_up_with_whole_outputs():
+    """One rank per visible GPU: the NVLink exchange inside a replayed CUDA graph and the NCCL
+    all-gather of the C ABI, both bit for bit against each shard recomputed locally."""
+    world = min(torch.cuda.device_count(), 8)
+    world = 1 << (world.bit_length() - 1)  # 2, 4 or 8
+    script = os.path.join(os.path.dirname(__file__), "exchange_ranks.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world, "--master-addr",
+           "127.0.0.1", "--master-port", "29533", script]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
-    assert done.stdout.count("exchange ok") == 2
+    assert done.stdout.count("exchange ok") == world
+    assert done.stdout.count("all-gather ok") == world
