@@ -289,6 +289,56 @@ ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream);
 ishi_status ishi_exchange_debug_expect(ishi_exchange *ex, unsigned launches_ahead);
 void ishi_exchange_destroy(ishi_exchange *ex);
 
+/* ---- GGUF container ----------------------------------------------------------------------------
+ *
+ * GGUFFile (Sources/IshizukiKit/Config/GGUFFile.swift:179-397): header, metadata and tensor table
+ * of a .gguf file, the tensor data left on disk until a tensor is asked for. Host only (no GPU
+ * needed) except ishi_gguf_upload_tensor. The reference's refusals are kept: versions other than
+ * 2 and 3, implausible counts and lengths, ranks outside 1...4, unknown tensor types, shapes that
+ * are not whole blocks, an alignment that is not a power of two. */
+typedef struct ishi_gguf ishi_gguf;
+typedef struct ishi_gguf_tensor_info {
+  const char *name;   /* valid while the file is open */
+  int32_t rank;       /* 1...4 */
+  int64_t shape[4];   /* row-major (the file stores the fastest-varying dimension first): a
+                         [5120, 248320] table in the file reads as 248320 rows of 5120 here */
+  int32_t ggml_type;
+  int64_t offset;     /* relative to ishi_gguf_data_offset */
+  int64_t byte_count;
+} ishi_gguf_tensor_info;
+/* error_out (may be NULL) receives the reason when the file is refused. */
+ishi_status ishi_gguf_open(const char *path, ishi_gguf **out, char *error_out, size_t error_len);
+void ishi_gguf_close(ishi_gguf *g);
+const char *ishi_gguf_last_error(const ishi_gguf *g);
+uint32_t ishi_gguf_version(const ishi_gguf *g);
+int64_t ishi_gguf_data_offset(const ishi_gguf *g);
+int64_t ishi_gguf_alignment(const ishi_gguf *g);
+int64_t ishi_gguf_tensor_count(const ishi_gguf *g);
+int64_t ishi_gguf_find_tensor(const ishi_gguf *g, const char *name); /* index, or -1 */
+ishi_status ishi_gguf_tensor(const ishi_gguf *g, int64_t index, ishi_gguf_tensor_info *out);
+/* GGMLType.blockSize / typeSize / name for every type of the file format (GGUFFile.swift:44-113,
+ * pinned by Tests/IshizukiKitTests/GGUFTests.swift:17-35); 0 / NULL for an unknown id. */
+int ishi_gguf_type_block_size(int ggml_type);
+int ishi_gguf_type_size(int ggml_type);
+const char *ishi_gguf_type_name(int ggml_type);
+/* Metadata (GGUFValue): kind is 0 when the key is absent, else 1 uint, 2 int, 3 float, 4 bool,
+ * 5 string, 6 array. The int getter converts like GGUFValue.intValue. */
+int64_t ishi_gguf_metadata_count(const ishi_gguf *g);
+const char *ishi_gguf_metadata_key(const ishi_gguf *g, int64_t index);
+int ishi_gguf_metadata_kind(const ishi_gguf *g, const char *key);
+ishi_status ishi_gguf_metadata_int(const ishi_gguf *g, const char *key, int64_t *out);
+ishi_status ishi_gguf_metadata_float(const ishi_gguf *g, const char *key, double *out);
+const char *ishi_gguf_metadata_string(const ishi_gguf *g, const char *key);
+int64_t ishi_gguf_metadata_array_length(const ishi_gguf *g, const char *key); /* -1: not an array */
+ishi_status ishi_gguf_metadata_array_int(const ishi_gguf *g, const char *key, int64_t index, int64_t *out);
+const char *ishi_gguf_metadata_array_string(const ishi_gguf *g, const char *key, int64_t index);
+/* GGUFFile.data(for:): the bytes of one tensor into host memory. */
+ishi_status ishi_gguf_read_tensor(ishi_gguf *g, int64_t index, void *dst_host, int64_t dst_bytes);
+/* The same into device memory (the blocks a projection is created from, GGUFWeights.load,
+ * Sources/IshizukiKit/Core/GGUFWeights.swift:47-85), through page-locked staging; returns when the
+ * last copy has been issued and its staging buffer is free again. */
+ishi_status ishi_gguf_upload_tensor(ishi_gguf *g, int64_t index, void *dst_dev, int64_t dst_bytes, void *stream);
+
 /* ---- N-sharded projections: one NCCL all-gather per projection --------------------------------
  *
  * The plain way to assemble an N-sharded projection (no counterpart in the single-GPU reference):

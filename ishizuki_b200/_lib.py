@@ -19,6 +19,11 @@ OUT_TRANSPOSED = 1
 EXCHANGE_HANDLE_BYTES = 128
 
 
+class GGUFTensorInfo(ctypes.Structure):
+    _fields_ = [("name", c_char_p), ("rank", c_int32), ("shape", c_int64 * 4), ("ggml_type", c_int32),
+                ("offset", c_int64), ("byte_count", c_int64)]
+
+
 class WeightDesc(ctypes.Structure):
     _fields_ = [
         ("kind", c_int32), ("ggml_type", c_int32), ("bits", c_int32), ("group_size", c_int32),
@@ -62,6 +67,29 @@ SIGNATURES = {
     "ishi_ggml_block_size": (c_int, [c_int]),
     "ishi_ggml_type_size": (c_int, [c_int]),
     "ishi_q4k_matmul_few_static": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "ishi_gguf_open": (c_int, [c_char_p, POINTER(c_void_p), c_char_p, ctypes.c_size_t]),
+    "ishi_gguf_close": (None, [c_void_p]),
+    "ishi_gguf_last_error": (c_char_p, [c_void_p]),
+    "ishi_gguf_version": (ctypes.c_uint32, [c_void_p]),
+    "ishi_gguf_data_offset": (c_int64, [c_void_p]),
+    "ishi_gguf_alignment": (c_int64, [c_void_p]),
+    "ishi_gguf_tensor_count": (c_int64, [c_void_p]),
+    "ishi_gguf_find_tensor": (c_int64, [c_void_p, c_char_p]),
+    "ishi_gguf_tensor": (c_int, [c_void_p, c_int64, POINTER(GGUFTensorInfo)]),
+    "ishi_gguf_type_block_size": (c_int, [c_int]),
+    "ishi_gguf_type_size": (c_int, [c_int]),
+    "ishi_gguf_type_name": (c_char_p, [c_int]),
+    "ishi_gguf_metadata_count": (c_int64, [c_void_p]),
+    "ishi_gguf_metadata_key": (c_char_p, [c_void_p, c_int64]),
+    "ishi_gguf_metadata_kind": (c_int, [c_void_p, c_char_p]),
+    "ishi_gguf_metadata_int": (c_int, [c_void_p, c_char_p, POINTER(c_int64)]),
+    "ishi_gguf_metadata_float": (c_int, [c_void_p, c_char_p, POINTER(ctypes.c_double)]),
+    "ishi_gguf_metadata_string": (c_char_p, [c_void_p, c_char_p]),
+    "ishi_gguf_metadata_array_length": (c_int64, [c_void_p, c_char_p]),
+    "ishi_gguf_metadata_array_int": (c_int, [c_void_p, c_char_p, c_int64, POINTER(c_int64)]),
+    "ishi_gguf_metadata_array_string": (c_char_p, [c_void_p, c_char_p, c_int64]),
+    "ishi_gguf_read_tensor": (c_int, [c_void_p, c_int64, c_void_p, c_int64]),
+    "ishi_gguf_upload_tensor": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "ishi_group_unique_id": (c_int, [c_void_p]),
     "ishi_group_create": (c_int, [c_void_p, c_int, c_int, c_int, POINTER(c_void_p)]),
     "ishi_group_last_error": (c_char_p, [c_void_p]),

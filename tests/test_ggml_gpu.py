@@ -284,3 +284,37 @@ def test_misaligned_rotation_signs_are_refused_before_anything_runs():
     with pytest.raises(IshizukiError) as err:
         PackedLinear(dev(w), dev(sb).view(torch.bfloat16), dev(bb).view(torch.bfloat16), signs[1:], 128, groupSize=128, bits=2)
     assert err.value.status == _lib.E_INVALID
+
+
+def test_a_projection_and_an_embedding_read_straight_off_a_gguf_file(tmp_path):
+    """Tests/IshizukiKitTests/GGUFWeightsTests.swift:119-177: an IQ2_S projection and an IQ1_M
+    embedding table out of a GGUF file, against decode-then-multiply."""
+    gguf = pytest.importorskip("gguf")
+    from ishizuki_b200.gguf_file import GGUFFile
+
+    rng = np.random.default_rng(33)
+    hidden, vocab = 256, 16
+    table = synth.ggml_blocks(rng, int(GGMLType.iq1M), vocab, hidden)
+    up = synth.ggml_blocks(rng, int(GGMLType.iq2S), hidden, hidden)
+    path = tmp_path / "modules.gguf"
+    w = gguf.GGUFWriter(str(path), "qwen35")
+    w.add_tensor("token_embd.weight", table.reshape(vocab, -1), raw_dtype=gguf.GGMLQuantizationType(29))
+    w.add_tensor("blk.0.ffn_up.weight", up.reshape(hidden, -1), raw_dtype=gguf.GGMLQuantizationType(22))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+    f = GGUFFile(path)
+    blocks = f.blocks("blk.0.ffn_up.weight")
+    assert (blocks.type, blocks.shape) == (GGMLType.iq2S, (hidden, hidden))
+    assert np.array_equal(blocks.bytes.cpu().numpy(), up)
+    lin = PackedLinear(ggml=blocks)
+    x = synth.activations(rng, 1, hidden)
+    want32, _ = oracle.ggml_matmul(int(GGMLType.iq2S), up, x, hidden)
+    assert rel_err(lin(dev(x)).cpu().numpy(), want32) < TOL
+
+    emb = f.blocks("token_embd.weight")
+    rows = GGMLKernels.gather(torch.tensor([3, 11]).cuda(), emb.bytes, emb.type, hidden, dtype=torch.float32)
+    full = oracle.dequantize(int(GGMLType.iq1M), table).reshape(vocab, hidden)
+    assert same_bits(rows.cpu().numpy(), full[[3, 11]])
