@@ -81,11 +81,15 @@ struct FragAffine {
   // after_loads() runs once, when the first batch of loads is in flight and before their values are
   // used (the kernel issues its first weight copies there, behind the activations).
   template <class F>
-  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
+  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, uint32_t xbar,
+                                                 volatile int *abort_word, F &&after_loads) {
+    (void)xbar;
+    (void)abort_word;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int tasks = uc * 8;
     constexpr int kBatch = 8;
     const __half *xl = a.x + (long long)ub0 * 256 + lane * 8;
+    if (warp >= tasks) after_loads();  // a warp without a task
     for (int i0 = warp; i0 < tasks; i0 += nw * kBatch) {
       uint4 v[kBatch];
 #pragma unroll
@@ -159,8 +163,9 @@ struct FragAffine {
   // One tile against the activations of its unit. acc: the warp's C fragment (MODE 0) or this
   // lane's partial dot products of rows g (acc[0]) and g + 8 (acc[2]) (MODE 1).
   template <int MODE>
-  static __device__ __forceinline__ void unit(float (&acc)[4], const FragArgs &a, uint32_t tile, uint32_t xu, int g,
-                                              int t, int lane) {
+  static __device__ __forceinline__ void unit(float (&acc)[4], const FragArgs &a, uint32_t tile, uint32_t xbase, int uq,
+                                              int g, int t, int lane) {
+    const uint32_t xu = xbase + (uint32_t)uq * kXBytes;
     // scales and biases of the two rows: kGroups halfwords of each, packed in pairs
     uint32_t hdr0[kRowHeader / 4], hdr1[kRowHeader / 4];
     if (kRowHeader == 8) {

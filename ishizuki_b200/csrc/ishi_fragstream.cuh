@@ -173,7 +173,8 @@ __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_b
 // partial panels of the cluster's CTAs, a control block (inbox mbarriers, arrival counters,
 // progress words, abort word), the warps' rings
 // control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @256, done [PP] @288,
-// abort @304, phases used of every inbox mbarrier [PP][2G] @320, ring mbarriers [warp][kFragRing] @512
+// abort @304, phases used of every inbox mbarrier [PP][2G] @320, the activation staging mbarrier @448,
+// ring mbarriers [warp][kFragRing] @512
 constexpr uint32_t kFragCtrlBytes = 1024;
 __host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int G, int S, int tile_bytes) {
   return (size_t)umax * xbytes + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
@@ -333,7 +334,9 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
     for (int i = 0; i < PP * kFragRed; ++i) cnt[i] = 0;
     for (int i = 0; i < PP; ++i) done[i] = 0;
     *abort_word = 0;
+    mbar_init_u32(ctrl + 448u, 1);  // activation staging (formats that copy x with the bulk copy engine)
     mbar_fence_init();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   // Shared memory of another CTA may be written only once that CTA runs and has set up its
   // barriers: every CTA arrives here, and waits before its first panel.
@@ -393,18 +396,18 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
         }
         if (!ok) *a.err = 2;  // give up: the result is wrong, the error word tells the host
       }
-      __syncthreads();
     }
   }
+  __syncthreads();  // the control block is set up for every warp; the other GPUs' rows have arrived
   ISHI_STAMP(2);
 
   // activations of the column range into fragment order (all warps)
-  Fmt::stage_x(a, xfrag, ub0, uc, [&]() { ISHI_STAMP(8); });
+  Fmt::stage_x(a, xfrag, ub0, uc, ctrl + 448u, abort_word, [&]() { ISHI_STAMP(8); });
   ISHI_STAMP(3);
   __syncthreads();
   ISHI_STAMP(4);
   // shared-memory loads are plain asm the compiler may move; tie their addresses to the waits
-  const uint32_t xf = stage_acquire(xfrag) + (uint32_t)wu * Fmt::kXBytes;
+  const uint32_t xf = stage_acquire(xfrag);
 
   if (S > 1) cluster_wait_relaxed();
   ISHI_STAMP(5);
@@ -433,7 +436,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     {
-      uint32_t xq = xf;
+      int uq = wu;  // the unit's index in the column range
       for (int qi = 0; qi < per; ++qi) {
         ISHI_CLOCK(c0);
         if (!mbar_wait_u32(wbar + 8u * c_idx, c_phase, abort_word)) *a.err = 1;  // this slot has landed
@@ -441,12 +444,12 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
         if (i == 0 && qi == 0) ISHI_STAMP(6);
         ISHI_CLOCK(c1);
         fetch();                         // refill the previous slot
-        Fmt::template unit<MODE>(acc, a, stage_acquire(c_slot), xq, g, t, lane);
+        Fmt::template unit<MODE>(acc, a, stage_acquire(c_slot), xf, uq, g, t, lane);
         values_ready(acc[0], acc[1], acc[2], acc[3]);
         ISHI_CLOCK(c2);
         ISHI_SPENT(16, c0, c1);
         ISHI_SPENT(17, c1, c2);
-        xq += (uint32_t)Wu * Fmt::kXBytes;
+        uq += Wu;
         c_slot += kStride;
         if (++c_idx == kFragRing) {
           c_idx = 0;
