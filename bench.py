@@ -357,12 +357,17 @@ def format_table(peak: float) -> dict:
 
     table = {}
     n, k, copies = 17408, 5120, 4
+    # ISHI_BENCH_FORMATS=name[,name]: only these rows of the first group (profiler captures of one format)
+    only = [f for f in os.environ.get("ISHI_BENCH_FORMATS", "").split(",") if f]
+    row_counts = [int(r) for r in os.environ.get("ISHI_BENCH_ROWS", "1,8").split(",")]  # activation rows M
     for fmt in ("q4_k", "affine4_g64", "ternary2_g128_h128", "iq2_xs", "q6_k"):
+        if only and fmt not in only:
+            continue
         lins = [make(fmt, n, k) for _ in range(copies)]
         row = {"weight_mb": lins[0].weightBytes / 1e6}
-        for m in (1, 8):
+        for m in row_counts:
             row["m%d" % m] = measure(lins, m, k)
-        if fmt in ("q4_k", "affine4_g64"):
+        if fmt in ("q4_k", "affine4_g64") and not only:
             # the single-row CUDA-core variant beside the tensor-core kernel (ISHI_ROUTE_GEMV)
             BonsaiRuntime.route = _lib.ROUTE_GEMV
             try:
@@ -372,6 +377,8 @@ def format_table(peak: float) -> dict:
         table[fmt] = row
         del lins
         torch.cuda.empty_cache()
+    if only:
+        return table
     # one row on CUDA cores beside the tensor-core kernel on the smallest and the tallest projection
     for name, n_, k_ in (("q4_k_kv_1024x5120", 1024, 5120), ("q4_k_down_5120x17408", 5120, 17408)):
         lins = [make("q4_k", n_, k_) for _ in range(8 if n_ < 2048 else 4)]
@@ -685,8 +692,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="default: 64 (stack), 8 (mlp)")
-    ap.add_argument("--workload", default="stack", choices=["stack", "mlp"],
-                    help="stack: all seven projections of every layer (the headline); mlp: gate/up/down only")
+    ap.add_argument("--workload", default="stack", choices=["stack", "mlp", "formats"],
+                    help="stack: all seven projections of every layer (the headline); mlp: gate/up/down only; "
+                         "formats: only the per-format side table (one GPU)")
     ap.add_argument("--unfused", action="store_true", help="one launch per matrix instead of stacked q+k+v and gate+up")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
@@ -698,6 +706,10 @@ def main() -> None:
         if int(os.environ.get("RANK", "0")) != 0:
             return
         print(json.dumps(run_reference(args)), flush=True)
+        return
+    if args.workload == "formats":
+        peak, kind = measured_peak()
+        print(json.dumps({"formats": format_table(peak), "peak": peak, "peak_kind": kind}), flush=True)
         return
     out = run_ours(args)
     if out is not None:

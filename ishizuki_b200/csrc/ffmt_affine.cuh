@@ -81,10 +81,7 @@ struct FragAffine {
   // after_loads() runs once, when the first batch of loads is in flight and before their values are
   // used (the kernel issues its first weight copies there, behind the activations).
   template <class F>
-  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, uint32_t xbar,
-                                                 volatile int *abort_word, F &&after_loads) {
-    (void)xbar;
-    (void)abort_word;
+  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int tasks = uc * 8;
     constexpr int kBatch = 8;

@@ -89,57 +89,56 @@ struct FragQ4K {
     return (uint16_t)(tile_byte(s, p, u, 2 * hw) | ((uint32_t)tile_byte(s, p, u, 2 * hw + 1) << 8));
   }
 
-  // Activations of the CTA's column range: one bulk copy per activation row straight from x (the
-  // row's units are contiguous there; rows past M are cleared), counted on the staging mbarrier
-  // xbar; then a warp task per (unit, row) adds up x over every sub-block for the minimum term.
-  // after_loads() runs once the copies are on their way. Q4_K has no input rotation.
+  // Activations of the CTA's column range. A warp task is (unit, activation row): lane l loads
+  // k = 8l .. 8l + 7 of it, stores them as they lie in x (rows past M as zeros) and the warp adds up
+  // every sub-block for the minimum term. after_loads() runs once, when the first batch of loads is
+  // in flight. Q4_K has no input rotation.
   static __device__ __forceinline__ uint32_t row_stride(const FragArgs &a) { return (uint32_t)a.umax * 512u + 64u; }
 
   template <class F>
-  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, uint32_t xbar,
-                                                 volatile int *abort_word, F &&after_loads) {
+  static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const uint32_t R = row_stride(a), sums = xfrag + 8u * R;
-    const uint32_t row_bytes = (uint32_t)uc * 512u;
-    if (threadIdx.x == 0) mbar_arrive_expect_tx_u32(xbar, (uint32_t)a.M * row_bytes);
-    if (lane == 0)
-      for (int r = warp; r < a.M; r += nw)
-        bulk_g2s_u32(xfrag + (uint32_t)r * R, a.x + (long long)r * a.K + (long long)ub0 * 256, row_bytes, xbar);
-    if (a.M < 8) {
-      // rows past M read as zero (plain stores: nothing else writes there)
-      const int vecs = uc * 32;  // 16-byte pieces of a row
-      for (int i = threadIdx.x; i < (8 - a.M) * vecs; i += blockDim.x) {
-        const int r = a.M + i / vecs, c = i - (r - a.M) * vecs;
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(xfrag + (uint32_t)r * R + (uint32_t)c * 16u), "r"(0u)
-                     : "memory");
+    const int tasks = uc * 8, jj = lane >> 3;
+    constexpr int kBatch = 4;
+    const __half *xl = a.x + (long long)ub0 * 256 + lane * 8;
+    if (warp >= tasks) after_loads();  // a warp without a task
+    for (int i0 = warp; i0 < tasks; i0 += nw * kBatch) {
+      uint4 v[kBatch];
+#pragma unroll
+      for (int e = 0; e < kBatch; ++e) {
+        const int i = i0 + e * nw;
+        v[e] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < tasks && (i & 7) < a.M)
+          v[e] = __ldg(reinterpret_cast<const uint4 *>(xl + (long long)(i & 7) * a.K + (i >> 3) * 256));
       }
-    }
-    after_loads();
-    if (!mbar_wait_u32(xbar, 0u, abort_word)) *a.err = 1;
-    __syncthreads();  // the cleared rows are visible to the warps that add them up
-    const int jj = lane >> 3;
-    for (int i = warp; i < uc * 8; i += nw) {
-      const int r = i & 7, u = i >> 3;
-      const uint4 v = lds128(xfrag + (uint32_t)r * R + (uint32_t)u * 512u + (uint32_t)lane * 16u);  // k = 8 * lane .. 8 * lane + 7
-      const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
-      const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
-      const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&v.z));
-      const float2 f3 = __half22float2(*reinterpret_cast<const __half2 *>(&v.w));
-      float s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      const float o = __shfl_xor_sync(0xffffffffu, s, 4);
-      const uint32_t base = sums + (uint32_t)u * kSumBytes;
-      if ((lane & 7) == 0) {
-        // sub-blocks 2t' and 2t' + 1 (t' = lane / 8) of activation row r, as fp16 hi + lo: the B
-        // fragment of the minimum-term MMA, whose k index runs over sub-blocks
-        const __half h0 = __float2half_rn(s), h1 = __float2half_rn(o);
-        const __half l0 = __float2half_rn(s - __half2float(h0)), l1 = __float2half_rn(o - __half2float(h1));
-        sts64(base + (uint32_t)(r * 4 + jj) * 8u, (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16),
-              (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16));
+      if (i0 == warp) after_loads();
+#pragma unroll
+      for (int e = 0; e < kBatch; ++e) {
+        const int i = i0 + e * nw;
+        if (i >= tasks) break;
+        const int r = i & 7, u = i >> 3;
+        sts128u(xfrag + (uint32_t)r * R + (uint32_t)u * 512u + (uint32_t)lane * 16u, v[e]);
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&v[e].x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&v[e].y));
+        const float2 f2 = __half22float2(*reinterpret_cast<const __half2 *>(&v[e].z));
+        const float2 f3 = __half22float2(*reinterpret_cast<const __half2 *>(&v[e].w));
+        float s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        const float o = __shfl_xor_sync(0xffffffffu, s, 4);
+        const uint32_t base = sums + (uint32_t)u * kSumBytes;
+        if ((lane & 7) == 0) {
+          // sub-blocks 2t' and 2t' + 1 (t' = lane / 8) of activation row r, as fp16 hi + lo: the B
+          // fragment of the minimum-term MMA, whose k index runs over sub-blocks
+          const __half h0 = __float2half_rn(s), h1 = __float2half_rn(o);
+          const __half l0 = __float2half_rn(s - __half2float(h0)), l1 = __float2half_rn(o - __half2float(h1));
+          sts64(base + (uint32_t)(r * 4 + jj) * 8u, (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16),
+                (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16));
+        }
+        if (r == 0 && (lane & 3) == 0)  // fp32 sums of activation row 0 (the single-row kernel's minimum term)
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + 256u + (uint32_t)(lane >> 2) * 4u), "f"(s) : "memory");
       }
-      if (r == 0 && (lane & 3) == 0)  // fp32 sums of activation row 0 (the single-row kernel's minimum term)
-        asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + 256u + (uint32_t)(lane >> 2) * 4u), "f"(s) : "memory");
     }
   }
 

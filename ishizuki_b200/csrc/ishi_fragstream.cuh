@@ -173,8 +173,7 @@ __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_b
 // partial panels of the cluster's CTAs, a control block (inbox mbarriers, arrival counters,
 // progress words, abort word), the warps' rings
 // control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @256, done [PP] @288,
-// abort @304, phases used of every inbox mbarrier [PP][2G] @320, the activation staging mbarrier @448,
-// ring mbarriers [warp][kFragRing] @512
+// abort @304, phases used of every inbox mbarrier [PP][2G] @320, ring mbarriers [warp][kFragRing] @512
 constexpr uint32_t kFragCtrlBytes = 1024;
 __host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int G, int S, int tile_bytes) {
   return (size_t)umax * xbytes + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
@@ -326,17 +325,15 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   // Let the next kernel on the stream start its own prologue as SMs fall free.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < PP * 2 * G; ++i) {
+  if (threadIdx.x < 32) {  // the control block, a word or a barrier per lane of warp 0
+    for (int i = threadIdx.x; i < PP * 2 * G; i += 32) {
       mbar_init(bars + i, 1);
       uses[i] = 0;
     }
-    for (int i = 0; i < PP * kFragRed; ++i) cnt[i] = 0;
-    for (int i = 0; i < PP; ++i) done[i] = 0;
-    *abort_word = 0;
-    mbar_init_u32(ctrl + 448u, 1);  // activation staging (formats that copy x with the bulk copy engine)
+    if ((int)threadIdx.x < PP * kFragRed) cnt[threadIdx.x] = 0;
+    if ((int)threadIdx.x < PP) done[threadIdx.x] = 0;
+    if (threadIdx.x == 0) *abort_word = 0;
     mbar_fence_init();
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   // Shared memory of another CTA may be written only once that CTA runs and has set up its
   // barriers: every CTA arrives here, and waits before its first panel.
@@ -402,7 +399,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   ISHI_STAMP(2);
 
   // activations of the column range into fragment order (all warps)
-  Fmt::stage_x(a, xfrag, ub0, uc, ctrl + 448u, abort_word, [&]() { ISHI_STAMP(8); });
+  Fmt::stage_x(a, xfrag, ub0, uc, [&]() { ISHI_STAMP(8); });
   ISHI_STAMP(3);
   __syncthreads();
   ISHI_STAMP(4);
