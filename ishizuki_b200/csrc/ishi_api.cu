@@ -22,6 +22,7 @@ using namespace ishi;
 namespace ishi {
 // the per-format kernel tables (frag_*.cu, row_*.cu)
 const FragOps *frag_ops_q4k();
+const FragOps *frag_ops_q6k();
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
 const FragOps *frag_ops_affine2(int group_size, bool bf16);
 const RowOps *row_ops_ggml(int type);
@@ -367,7 +368,11 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
 
 // The fragment decoder that serves a weight, or null (the tcgen05 kernel then takes it).
 const FragOps *frag_ops_for(const ishi_weight_desc &d) {
-  if (d.kind == ISHI_KIND_GGML) return d.ggml_type == ISHI_GGML_Q4_K ? frag_ops_q4k() : nullptr;
+  if (d.kind == ISHI_KIND_GGML) {
+    if (d.ggml_type == ISHI_GGML_Q4_K) return frag_ops_q4k();
+    if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
+    return nullptr;
+  }
   if (d.scale_dtype != ISHI_DT_F16 && d.scale_dtype != ISHI_DT_BF16) return nullptr;
   const bool bf16 = d.scale_dtype == ISHI_DT_BF16;
   if (d.bits == 4) return frag_ops_affine4(d.group_size, bf16);

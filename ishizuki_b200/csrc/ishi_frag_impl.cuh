@@ -11,7 +11,10 @@ template <class Fmt>
 struct FragOpsOf {
   static cudaError_t configure(int max_smem) {
     cudaError_t e = cudaFuncSetAttribute(frag_kernel<Fmt, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(frag_kernel<Fmt, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if constexpr (Fmt::kRowMode) {
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(frag_kernel<Fmt, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    }
     return e;
   }
 
@@ -51,7 +54,10 @@ struct FragOpsOf {
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = l.early ? 2 : 1;
-    if (l.mode == 1) return cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 1>, args);
+    // a format without a CUDA-core variant for one activation row runs that row through the MMA path
+    if constexpr (Fmt::kRowMode) {
+      if (l.mode == 1) return cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 1>, args);
+    }
     return cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 0>, args);
   }
 

@@ -25,11 +25,21 @@ def dev(a: np.ndarray) -> torch.Tensor:
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
+def _projection(fmt, rng, n, k):
+    if fmt == "q4_k":
+        return PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
+    if fmt == "q6_k":
+        return PackedLinear(ggml=GGUFBlocks(dev(synth.q6k_blocks(rng, n, k)), GGMLType.q6K, (n, k)))
+    w, s, b = synth.affine_pack(rng, n, k, 4, 64, np.float16)
+    return PackedLinear(dev(w), dev(s), dev(b), None, 0, groupSize=64, bits=4)
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "affine4"])
 @pytest.mark.parametrize("rows", [1, 5, 8])
-def test_single_rank_exchange_matches_projection(rows):
+def test_single_rank_exchange_matches_projection(rows, fmt):
     rng = np.random.default_rng(rows)
     n, k = 1000, 2048  # a ragged last panel
-    lin = PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
+    lin = _projection(fmt, rng, n, k)
     ex = OutputExchange(4 << 20)
     off_a, view_a = ex.reserve(n)
     off_b, view_b = ex.reserve(n)

@@ -210,6 +210,21 @@ def test_stacked_projections_are_one_launch_with_the_same_products(sizes):
             assert rel_err(piece.cpu().numpy(), want32) < TOL
 
 
+def test_stacked_q6k_matrices():
+    """Q6_K has a fragment decoder too: matrices that share an input stack into one launch."""
+    rng = np.random.default_rng(12)
+    k, sizes = 1024, (48, 200)
+    parts = [synth.q6k_blocks(rng, n, k) for n in sizes]
+    fused = FusedLinear([GGUFBlocks(dev(b), GGMLType.q6K, (n, k)) for b, n in zip(parts, sizes)])
+    x = synth.activations(rng, 8, k)
+    y = fused(dev(x))
+    torch.cuda.synchronize()
+    fused.ctx.poll()
+    for piece, blocks, n in zip(fused.split(y), parts, sizes):
+        want32, _ = oracle.ggml_matmul(int(GGMLType.q6K), blocks, x, n)
+        assert rel_err(piece.cpu().numpy(), want32) < TOL
+
+
 def test_stacked_affine_packs():
     rng = np.random.default_rng(9)
     k, sizes = 2048, (256, 100)
@@ -228,9 +243,10 @@ def test_stacking_guards():
     b = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 1024)), GGMLType.q4K, (32, 1024))
     with pytest.raises(ValueError):
         FusedLinear([a, b])  # different input widths
-    q6 = [GGUFBlocks(dev(synth.q6k_blocks(rng, 32, 512)), GGMLType.q6K, (32, 512)) for _ in range(2)]
+    other = [GGUFBlocks(dev(synth.ggml_blocks(rng, int(GGMLType.iq4Xs), 32, 512)), GGMLType.iq4Xs, (32, 512))
+             for _ in range(2)]
     with pytest.raises(IshizukiError) as err:
-        FusedLinear(q6)  # no fragment decoder: cannot be stacked
+        FusedLinear(other)  # no fragment decoder: cannot be stacked
     assert err.value.status == _lib.E_UNSUPPORTED
 
 
