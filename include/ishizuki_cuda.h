@@ -357,7 +357,8 @@ const char *ishi_group_last_error(const ishi_group *g);
 /* x [rows, k] against this rank's shard p (n_local rows, the same on every rank): y_all_dev is
  * fp16 [world * n_local][rows], rank r's rows at [r * n_local, (r + 1) * n_local), the transposed
  * form of ishi_projection_apply; the product writes this rank's slab in place and the all-gather
- * fills the rest, both on the stream. rows in 1...16. */
+ * fills the rest, both on the stream. rows in 1...16. Eager streams only: on a stream that is being
+ * captured into a CUDA graph the call returns ISHI_E_UNSUPPORTED (ishi_exchange_apply can be captured). */
 ishi_status ishi_projection_apply_sharded(ishi_group *g, ishi_projection *p, const void *x_dev, int rows,
                                           void *y_all_dev, void *stream);
 void ishi_group_destroy(ishi_group *g);

@@ -170,6 +170,17 @@ ishi_status ishi_projection_apply_sharded(ishi_group *g, ishi_projection *p, con
   if (g->broken || !g->comm) return group_fail(g, ISHI_E_NCCL, "the communicator is no longer usable");
   if (!x_dev || !y_all_dev) return group_fail(g, ISHI_E_INVALID, "null pointer");
   if (rows < 1 || rows > 16) return group_fail(g, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  // The collective is enqueued eagerly only: inside a stream capture the communicator's host-side
+  // progress (connection setup, asynchronous error polling) is not ordered by the graph.
+  if (g->world > 1) {
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capturing) != cudaSuccess) {
+      cudaGetLastError();
+      return group_fail(g, ISHI_E_CUDA, "cudaStreamIsCapturing failed");
+    }
+    if (capturing != cudaStreamCaptureStatusNone)
+      return group_fail(g, ISHI_E_UNSUPPORTED, "the sharded product with an all-gather cannot be captured in a CUDA graph");
+  }
   const int64_t n_local = ishi_projection_output_dim(p);
   // this rank's rows, transposed, straight into its slab of the gathered array
   __half *slab = static_cast<__half *>(y_all_dev) + (size_t)g->rank * n_local * rows;

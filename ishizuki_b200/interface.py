@@ -1,9 +1,8 @@
 """Host-side mirror of the reference's projection interface on top of the C ABI.
 
 The reference's host language is Swift; no Swift toolchain exists where this library is built
-and tested, so the same surface is written here in Python over ctypes (the Swift binding a
-maintainer would add is shown in INTEGRATION.md). Names, argument meaning and "declined"
-behaviour follow the reference:
+and tested, so the same surface is written here in Python over ctypes. Names, argument meaning
+and "declined" behaviour follow the reference:
 
   GGMLType, GGUFBlocks      Sources/IshizukiKit/Config/GGUFFile.swift:13-121,
                             Sources/IshizukiKit/Core/GGUFWeights.swift:13-26
