@@ -287,6 +287,13 @@ ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream);
  * bound (about a second), raises the context's error word and returns: this is how the
  * failure path of the bounded waits is exercised without hanging or faulting a GPU. */
 ishi_status ishi_exchange_debug_expect(ishi_exchange *ex, unsigned launches_ahead);
+/* Teardown in two steps, because the other ranks hold mappings of this rank's buffer and may
+ * still be storing into it: every rank calls ishi_exchange_disconnect (waits for its own launches,
+ * closes its mappings of the peers' buffers; apply is refused afterwards), the HOST then barriers
+ * across the ranks by whatever channel it has, and only then every rank calls
+ * ishi_exchange_destroy, which frees the buffer. destroy alone disconnects first, which is enough
+ * for a single rank. */
+ishi_status ishi_exchange_disconnect(ishi_exchange *ex);
 void ishi_exchange_destroy(ishi_exchange *ex);
 
 /* ---- GGUF container ----------------------------------------------------------------------------

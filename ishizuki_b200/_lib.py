@@ -103,6 +103,7 @@ SIGNATURES = {
     "ishi_exchange_apply": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p]),
     "ishi_exchange_wait": (c_int, [c_void_p, c_void_p]),
     "ishi_exchange_debug_expect": (c_int, [c_void_p, ctypes.c_uint]),
+    "ishi_exchange_disconnect": (c_int, [c_void_p]),
     "ishi_exchange_destroy": (None, [c_void_p]),
 }
 

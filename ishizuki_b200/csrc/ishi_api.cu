@@ -38,6 +38,7 @@ struct Workspace {
   unsigned int *counters = nullptr;
   uint8_t *tiles = nullptr;  // kernel-level calls re-tile the weight here on every call
   size_t scratch_floats = 0, n_counters = 0, tiles_bytes = 0;
+  mutable unsigned epoch = 0;  // the context's time-out count when the counters were last known to be zero
 };
 
 // Internal format id: the GGML type number, or 100 + bits for an affine pack.
@@ -56,7 +57,7 @@ struct RowPlan {
 struct FragPlan {
   bool ok = false;
   const FragOps *ops = nullptr;  // the format's kernels
-  int units = 0, S = 1, P = 0, NC = 1, Wu = 1, PP = 1, G = 1, umax = 0, tile_bytes = 0;
+  int units = 0, S = 1, P = 0, NC = 1, Wu = 1, PP = 1, G = 1, ring = 3, umax = 0, tile_bytes = 0;
   size_t smem = 0, tiles_bytes = 0;
   double cost = 0;
 };
@@ -70,6 +71,7 @@ struct ishi_ctx {
   int route = ISHI_ROUTE_AUTO;
   int crossover_rows = 0;
   int *err_host = nullptr;  // mapped pinned word the kernels raise on a timed-out wait
+  unsigned timeout_epoch = 0;  // time-outs seen by ishi_ctx_poll: arrival counters from before may be stale
   int *err_dev = nullptr;
   Workspace ws;                             // for the kernel-level entry points
   void *pin_x = nullptr, *pin_y = nullptr;  // pinned staging for apply_host
@@ -251,7 +253,10 @@ bool make_row_plan(const ishi_ctx *ctx, const ishi_weight_desc &d, RowPlan *pl) 
   return true;
 }
 
-ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t counters, size_t tiles) {
+// st: the stream of the call the workspace is for; fresh counters are cleared on it, so the
+// clearing is ordered before the call's kernels whatever kind of stream it is.
+ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t counters, size_t tiles,
+                             cudaStream_t st) {
   if (floats > ws->scratch_floats) {
     if (ws->scratch) cudaFree(ws->scratch);
     ws->scratch = nullptr;
@@ -264,8 +269,9 @@ ishi_status ensure_workspace(ishi_ctx *ctx, Workspace *ws, size_t floats, size_t
     ws->counters = nullptr;
     ws->n_counters = 0;
     ISHI_CUDA(ctx, cudaMalloc(&ws->counters, counters * sizeof(unsigned int)));
-    ISHI_CUDA(ctx, cudaMemset(ws->counters, 0, counters * sizeof(unsigned int)));
+    ISHI_CUDA(ctx, cudaMemsetAsync(ws->counters, 0, counters * sizeof(unsigned int), st));
     ws->n_counters = counters;
+    ws->epoch = ctx->timeout_epoch;
   }
   if (tiles > ws->tiles_bytes) {
     if (ws->tiles) cudaFree(ws->tiles);
@@ -330,6 +336,11 @@ ishi_status run_row(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int f
   a.y = static_cast<__half *>(y);
   a.ldy = ldy;
   a.out_transposed = (flags & ISHI_OUT_TRANSPOSED) ? 1 : 0;
+  if (ws.counters && ws.epoch != ctx->timeout_epoch) {
+    // a launch on this context timed out since these counters were last zero
+    ISHI_CUDA(ctx, cudaMemsetAsync(ws.counters, 0, ws.n_counters * sizeof(unsigned int), st));
+    ws.epoch = ctx->timeout_epoch;
+  }
   a.scratch = ws.scratch;
   a.counters = ws.counters;
   a.err = ctx->err_dev;
@@ -396,7 +407,7 @@ int max_frag_clusters(ishi_ctx *ctx, const FragOps *ops, int s, int warps, size_
 // Picks the K split S (= cluster size), the warps per panel and the panels a CTA works on in
 // parallel. The estimate counts tile times on the longest warp (panels of the fullest cluster x
 // units per warp), stretched where the warps outnumber what the issue slots sustain.
-bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
+bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl, std::vector<FragPlan> *all = nullptr) {
   const FragOps *ops = frag_ops_for(d);
   if (!ops) return false;
   const size_t budget = (size_t)std::min(kSmemPerSm, ctx->smem_optin) - 1024;
@@ -408,9 +419,9 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   const int P = (int)((d.n + kFragRows - 1) / kFragRows);
   // the kernel divides by multiplication, exact while (clusters + 1) * P < 2^32 / clusters
   if ((long long)P * (ctx->sm_count + 1) * ctx->sm_count >= (1ll << 32)) return false;
-  const char *force = getenv("ISHI_FRAG_PLAN");  // "S,per,PP" for tuning runs
-  int fs = 0, fper = 0, fpp = 0;
-  if (force) sscanf(force, "%d,%d,%d", &fs, &fper, &fpp);
+  const char *force = getenv("ISHI_FRAG_PLAN");  // "S,per,PP[,ring]" for tuning runs
+  int fs = 0, fper = 0, fpp = 0, fring = 0;
+  if (force) sscanf(force, "%d,%d,%d,%d", &fs, &fper, &fpp, &fring);
   for (int s = 1; s <= kFragMaxSplit && s <= units; ++s) {
     if (fs && s != fs) continue;
     const int umax = (units + s - 1) / s;
@@ -418,7 +429,7 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
     for (int per = per_min; per <= std::min(per_min + 2, kFragGroup); ++per) {
       if (fper && per != fper) continue;
       const int wu = (umax + per - 1) / per;
-      for (int pp = 1; pp <= 4 && wu * pp <= kFragMaxWarps; ++pp) {
+      for (int pp = 1; pp <= kFragMaxPanels && wu * pp <= kFragMaxWarps; ++pp) {
         if (fpp && pp != fpp) continue;
         FragPlan c;
         c.ops = ops;
@@ -430,11 +441,17 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
         c.Wu = wu;
         c.PP = pp;
         const int w = wu * pp;
-        for (c.G = 2; c.G >= 1; --c.G) {
-          c.smem = frag_smem_bytes(umax, xbytes, w, pp, c.G, s, tile_bytes);
-          if (c.smem <= budget) break;
-        }
-        if (c.G < 1) continue;
+        // the deepest tile ring that fits, then the larger inbox generation
+        bool fits = false;
+        for (int ring = fring ? fring : 3; ring >= (fring ? fring : 2) && !fits; --ring)
+          for (int gen = 2; gen >= 1 && !fits; --gen) {
+            const size_t need = frag_smem_bytes(umax, xbytes, w, pp, gen, s, tile_bytes, ring);
+            if (need <= budget) {
+              fits = true;
+              c.ring = ring, c.G = gen, c.smem = need;
+            }
+          }
+        if (!fits) continue;
         // one CTA per SM: two would stage the activations twice and split the issue slots
         c.NC = std::min(std::min(max_frag_clusters(ctx, ops, s, w, c.smem), ctx->sm_count / s), P);
         if (c.NC < 1) continue;
@@ -447,6 +464,8 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
         const double longest = 1.0 * rounds * per;
         c.cost = std::max(throughput, longest) + rounds * (0.05 * wu + (s > 1 ? 0.05 : 0.0)) + 0.02 * umax;
         c.ok = true;
+        c.tiles_bytes = (size_t)P * units * tile_bytes;
+        if (all) all->push_back(c);
         if (!best.ok || c.cost < best.cost) best = c;
       }
     }
@@ -454,8 +473,8 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl) {
   if (!best.ok) return false;
   best.tiles_bytes = (size_t)P * units * tile_bytes;
   if (getenv("ISHI_DEBUG_PLAN"))
-    fprintf(stderr, "ishi plan n=%lld k=%lld: split %d, clusters %d, warps %d x %d, generation %d, smem %zu\n",
-            (long long)d.n, (long long)d.k, best.S, best.NC, best.Wu, best.PP, best.G, best.smem);
+    fprintf(stderr, "ishi plan n=%lld k=%lld: split %d, clusters %d, warps %d x %d, generation %d, ring %d, smem %zu\n",
+            (long long)d.n, (long long)d.k, best.S, best.NC, best.Wu, best.PP, best.G, best.ring, best.smem);
   *pl = best;
   return true;
 }
@@ -535,6 +554,7 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.Wu = pl.Wu;
     a.PP = pl.PP;
     a.G = pl.G;
+    a.ring = pl.ring;
     a.inv_s = frag_inverse(pl.S);
     a.inv_nc = frag_inverse(pl.NC);
     a.inv_wu = frag_inverse(pl.Wu);
@@ -591,7 +611,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   FragPlan fp;
   if (make_frag_plan(ctx, d, &fp)) {
-    s = ensure_workspace(ctx, &ctx->ws, 0, 0, fp.tiles_bytes);
+    s = ensure_workspace(ctx, &ctx->ws, 0, 0, fp.tiles_bytes, st);
     if (s != ISHI_OK) return s;
     s = tile_weight_frag(ctx, fp, &d, 1, d.n, ctx->ws.tiles, st);
     if (s != ISHI_OK) return s;
@@ -608,7 +628,7 @@ ishi_status raw_product(ishi_ctx *ctx, const ishi_weight_desc &d, const void *x,
     }
     return fail(ctx, ISHI_E_SHAPE, "no launch plan fits shared memory");
   }
-  s = ensure_workspace(ctx, &ctx->ws, pl.scratch_floats, pl.counters, pl.tiles_bytes);
+  s = ensure_workspace(ctx, &ctx->ws, pl.scratch_floats, pl.counters, pl.tiles_bytes, st);
   if (s != ISHI_OK) return s;
   s = tile_weight(ctx, pl, d.n, ctx->ws.tiles, st);
   if (s != ISHI_OK) return s;
@@ -740,6 +760,7 @@ ishi_status ishi_ctx_poll(ishi_ctx *ctx) {
   volatile int *flag = ctx->err_host;
   if (*flag != 0) {
     *flag = 0;
+    ++ctx->timeout_epoch;  // CTAs that gave up skipped their arrivals: run_row clears the counters before their next use
     return fail(ctx, ISHI_E_TIMEOUT, "a kernel's bounded wait gave up; outputs of that launch are invalid");
   }
   return ISHI_OK;
@@ -869,6 +890,47 @@ ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x, int rows, const voi
 
 // ---- projection: the PackedLinear counterpart ---------------------------------------------------
 
+// The tile layout does not depend on the launch plan, so the plan can be chosen by measurement:
+// the planner's best candidates run a few times on the projection's own tiles (activations of
+// zeros, eight rows) and the fastest stays. The estimate alone is within ~15 % of the best plan.
+static void tune_frag_plan(ishi_ctx *ctx, ishi_projection *p, std::vector<FragPlan> *candidates) {
+  constexpr size_t kTuned = 8;
+  constexpr int kLaunches = 4;
+  if (candidates->size() < 2) return;
+  std::sort(candidates->begin(), candidates->end(), [](const FragPlan &a, const FragPlan &b) { return a.cost < b.cost; });
+  if (candidates->size() > kTuned) candidates->resize(kTuned);
+  __half *x = nullptr, *y = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  bool ok = cudaMalloc(&x, (size_t)8 * p->d.k * sizeof(__half)) == cudaSuccess &&
+            cudaMalloc(&y, (size_t)8 * p->d.n * sizeof(__half)) == cudaSuccess &&
+            cudaMemset(x, 0, (size_t)8 * p->d.k * sizeof(__half)) == cudaSuccess && cudaEventCreate(&e0) == cudaSuccess &&
+            cudaEventCreate(&e1) == cudaSuccess;
+  float best_ms = 0.f;
+  const FragPlan *best = nullptr;
+  for (size_t i = 0; ok && i < candidates->size(); ++i) {
+    const FragPlan &c = (*candidates)[i];
+    ok = run_frag(ctx, c, p->ws, p->d, x, 8, y, p->d.n, 0, false, true, false, 0) == ISHI_OK;  // warm-up
+    if (ok) ok = cudaEventRecord(e0, 0) == cudaSuccess;
+    for (int r = 0; ok && r < kLaunches; ++r) ok = run_frag(ctx, c, p->ws, p->d, x, 8, y, p->d.n, 0, false, true, false, 0) == ISHI_OK;
+    if (ok) ok = cudaEventRecord(e1, 0) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+    float ms = 0.f;
+    if (ok) ok = cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;
+    if (ok && (!best || ms < best_ms)) best = &c, best_ms = ms;
+  }
+  if (ok && best) {
+    p->frag = *best;
+    if (getenv("ISHI_DEBUG_PLAN"))
+      fprintf(stderr, "ishi plan n=%lld k=%lld measured: split %d, warps %d x %d, ring %d: %.2f us\n", (long long)p->d.n,
+              (long long)p->d.k, best->S, best->Wu, best->PP, best->ring, best_ms * 1e3f / kLaunches);
+  } else {
+    cudaGetLastError();  // keep the estimate's choice
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (x) cudaFree(x);
+  if (y) cudaFree(y);
+}
+
 ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
                                          ishi_projection **out) {
   if (!ctx || !out) return ISHI_E_INVALID;
@@ -900,19 +962,21 @@ ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *
   ishi_status s = ISHI_OK;
   // Re-tile the weight once, for the kernel this format runs on; the caller's buffers are not read
   // again afterwards.
-  if (make_frag_plan(ctx, p->d, &p->frag)) {
-    s = ensure_workspace(ctx, &p->ws, 0, 0, p->frag.tiles_bytes);
+  std::vector<FragPlan> candidates;
+  if (make_frag_plan(ctx, p->d, &p->frag, &candidates)) {
+    s = ensure_workspace(ctx, &p->ws, 0, 0, p->frag.tiles_bytes, 0);
     if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, descs, count, n_total, p->ws.tiles, 0);
+    if (s == ISHI_OK && !getenv("ISHI_NO_AUTOTUNE") && !getenv("ISHI_FRAG_PLAN")) tune_frag_plan(ctx, p, &candidates);
   } else if (count > 1) {
     delete p;
     return fail(ctx, ISHI_E_UNSUPPORTED, "only the warp-level kernel's formats can be stacked into one projection");
   } else if (make_row_plan(ctx, p->d, &p->plan)) {
-    s = ensure_workspace(ctx, &p->ws, p->plan.scratch_floats, p->plan.counters, p->plan.tiles_bytes);
+    s = ensure_workspace(ctx, &p->ws, p->plan.scratch_floats, p->plan.counters, p->plan.tiles_bytes, 0);
     if (s == ISHI_OK) s = tile_weight(ctx, p->plan, p->d.n, p->ws.tiles, 0);
   } else if (p->d.kind == ISHI_KIND_GGML && !row_ops(p->fmt)) {
     // a block format without a streaming kernel: keep a plain copy of the blocks
     p->generic = true;
-    s = ensure_workspace(ctx, &p->ws, 0, 0, (size_t)wb);
+    s = ensure_workspace(ctx, &p->ws, 0, 0, (size_t)wb, 0);
     if (s == ISHI_OK && cudaMemcpyAsync(p->ws.tiles, descs[0].weight_dev, (size_t)wb, cudaMemcpyDeviceToDevice, 0) != cudaSuccess)
       s = fail(ctx, ISHI_E_CUDA, "copying the blocks failed");
   } else {
@@ -1288,14 +1352,25 @@ ishi_status ishi_exchange_debug_expect(ishi_exchange *ex, unsigned launches_ahea
   return ISHI_OK;
 }
 
-void ishi_exchange_destroy(ishi_exchange *ex) {
-  if (!ex) return;
+ishi_status ishi_exchange_disconnect(ishi_exchange *ex) {
+  if (!ex) return ISHI_E_INVALID;
   cudaSetDevice(ex->ctx->device);
+  // this rank's launches may still be storing into the peers' buffers
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail(ex->ctx, ISHI_E_CUDA, "synchronising before the disconnect failed");
   for (int q = 0; q < ex->world; ++q) {
     if (q == ex->rank) continue;
     if (ex->peer_buf[q]) cudaIpcCloseMemHandle(ex->peer_buf[q]);
     if (ex->peer_words[q]) cudaIpcCloseMemHandle(ex->peer_words[q]);
+    ex->peer_buf[q] = nullptr;
+    ex->peer_words[q] = nullptr;
   }
+  ex->connected = false;
+  return ISHI_OK;
+}
+
+void ishi_exchange_destroy(ishi_exchange *ex) {
+  if (!ex) return;
+  ishi_exchange_disconnect(ex);
   if (ex->buf) cudaFree(ex->buf);
   if (ex->words) cudaFree(ex->words);
   delete ex;

@@ -10,10 +10,12 @@ namespace ishi {
 template <class Fmt>
 struct FragOpsOf {
   static cudaError_t configure(int max_smem) {
-    cudaError_t e = cudaFuncSetAttribute(frag_kernel<Fmt, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    cudaError_t e = cudaFuncSetAttribute(frag_kernel<Fmt, 0, kFragFewWarps>, attr, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(frag_kernel<Fmt, 0, kFragMaxWarps>, attr, max_smem);
     if constexpr (Fmt::kRowMode) {
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(frag_kernel<Fmt, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(frag_kernel<Fmt, 1, kFragFewWarps>, attr, max_smem);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(frag_kernel<Fmt, 1, kFragMaxWarps>, attr, max_smem);
     }
     return e;
   }
@@ -36,7 +38,10 @@ struct FragOpsOf {
     cudaLaunchAttribute at[2];
     fill(&cfg, at, sm_count, split, warps, smem);
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, frag_kernel<Fmt, 0>, &cfg) != cudaSuccess) {
+    const cudaError_t e = warps <= kFragFewWarps
+                              ? cudaOccupancyMaxActiveClusters(&n, frag_kernel<Fmt, 0, kFragFewWarps>, &cfg)
+                              : cudaOccupancyMaxActiveClusters(&n, frag_kernel<Fmt, 0, kFragMaxWarps>, &cfg);
+    if (e != cudaSuccess) {
       cudaGetLastError();
       return 0;
     }
@@ -55,10 +60,14 @@ struct FragOpsOf {
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = l.early ? 2 : 1;
     // a format without a CUDA-core variant for one activation row runs that row through the MMA path
+    const bool few = l.warps <= kFragFewWarps;
     if constexpr (Fmt::kRowMode) {
-      if (l.mode == 1) return cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 1>, args);
+      if (l.mode == 1)
+        return few ? cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 1, kFragFewWarps>, args)
+                   : cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 1, kFragMaxWarps>, args);
     }
-    return cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 0>, args);
+    return few ? cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 0, kFragFewWarps>, args)
+               : cudaLaunchKernelEx(&cfg, frag_kernel<Fmt, 0, kFragMaxWarps>, args);
   }
 
   static cudaError_t prepare(const FragSrc &src, int units, uint8_t *dst, int grid, cudaStream_t stream) {

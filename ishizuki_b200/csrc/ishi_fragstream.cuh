@@ -41,10 +41,15 @@ namespace ishi {
 
 constexpr int kFragRows = 16;
 #ifndef ISHI_FRAG_MAX_WARPS
-#define ISHI_FRAG_MAX_WARPS 20
+#define ISHI_FRAG_MAX_WARPS 24
 #endif
-constexpr int kFragMaxWarps = ISHI_FRAG_MAX_WARPS;  // 20 warps leave 96 registers per thread, 16 warps 128
-constexpr int kFragRing = 3;      // tiles per warp-private ring: two in flight while one is decoded
+// The kernel is compiled for two block sizes: up to kFragFewWarps warps with 96 registers per
+// thread (the decoders' loads then run further ahead of their use), and up to kFragMaxWarps with 80.
+constexpr int kFragMaxWarps = ISHI_FRAG_MAX_WARPS;
+constexpr int kFragFewWarps = 20;
+constexpr int kFragMaxRing = 4;   // most tiles per warp-private ring (FragArgs::ring of them are used:
+                                  // one is decoded while the others are in flight)
+constexpr int kFragMaxPanels = 8; // most panels a CTA works on in parallel
 constexpr int kFragGroup = 4;     // most units per warp the planner considers
 constexpr int kFragRed = 2;       // partial-tile slots per panel lane: a warp may run this many panels ahead of the slowest
 constexpr int kFragMaxGen = 4;    // most panels of a lane per generation of inbox slots
@@ -60,6 +65,7 @@ struct FragArgs {
   int M, N, K;
   int units, S, P, NC;  // NC clusters of S CTAs
   int Wu, PP, G;        // warps per panel, panels in parallel (Wu * PP warps per CTA), panels of a lane per inbox generation
+  int ring;             // tiles per warp-private ring, 2 ... kFragMaxRing
   // ceil(2^32 / d) for d = S, NC, Wu, PP, or 0 for d = 1: see frag_div()
   unsigned inv_s, inv_nc, inv_wu, inv_pp;
   int umax;             // most units in a column range
@@ -172,12 +178,13 @@ __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_b
 // shared memory of one CTA, in order: activations, the lanes' partial-tile slots, the inbox for the
 // partial panels of the cluster's CTAs, a control block (inbox mbarriers, arrival counters,
 // progress words, abort word), the warps' rings
-// control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @256, done [PP] @288,
-// abort @304, phases used of every inbox mbarrier [PP][2G] @320, ring mbarriers [warp][kFragRing] @512
-constexpr uint32_t kFragCtrlBytes = 1024;
-__host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int G, int S, int tile_bytes) {
+// control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @768, done [PP] @832,
+// abort @864, phases used of every inbox mbarrier [PP][2G] @512, ring mbarriers [warp][kFragMaxRing] @1024
+constexpr uint32_t kFragCtrlBytes = 2048;
+__host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int G, int S, int tile_bytes,
+                                                  int ring) {
   return (size_t)umax * xbytes + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
-         (size_t)W * kFragRing * frag_ring_stride(tile_bytes);
+         (size_t)W * ring * frag_ring_stride(tile_bytes);
 }
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
@@ -280,9 +287,9 @@ __device__ __forceinline__ void st_async128(uint32_t addr, float4 v, uint32_t mb
                : "memory");
 }
 
-// MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row.
-template <class Fmt, int MODE>
-__global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragArgs a) {
+// MODE 0: tensor-core (rows 1..8); MODE 1: CUDA-core FMA for a single row. MAXW: most warps of a block.
+template <class Fmt, int MODE, int MAXW>
+__global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kTile = Fmt::kTileBytes;
   constexpr uint32_t kStride = (uint32_t)((kTile + 127) & ~127);
@@ -300,13 +307,14 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;            // [PP][kFragRed][Wu][128 floats]
   const uint32_t inbox = red + (uint32_t)(W * kFragRed) * 512u;            // [PP][2G][S][128 floats]
   const uint32_t ctrl = inbox + (S > 1 ? (uint32_t)(PP * 2 * G * S) * 512u : 0u);
-  const uint32_t ring = ctrl + kFragCtrlBytes + (uint32_t)warp * kFragRing * kStride;
+  const int R = a.ring;  // tiles in this warp's ring
+  const uint32_t ring = ctrl + kFragCtrlBytes + (uint32_t)(warp * R) * kStride;
   uint8_t *ctrl_p = smem + (ctrl - xfrag);
   uint64_t *bars = reinterpret_cast<uint64_t *>(ctrl_p);                   // [PP][2G]
-  int *cnt = reinterpret_cast<int *>(ctrl_p + 256);                        // [PP][kFragRed] arrivals of the lane's warps
-  volatile int *done = reinterpret_cast<volatile int *>(ctrl_p + 288);     // [PP] panels of the lane whose partials were added
-  volatile int *abort_word = reinterpret_cast<volatile int *>(ctrl_p + 304);
-  volatile int *uses = reinterpret_cast<volatile int *>(ctrl_p + 320);     // [PP][2G] completed phases of each inbox mbarrier
+  int *cnt = reinterpret_cast<int *>(ctrl_p + 768);                        // [PP][kFragRed] arrivals of the lane's warps
+  volatile int *done = reinterpret_cast<volatile int *>(ctrl_p + 832);     // [PP] panels of the lane whose partials were added
+  volatile int *abort_word = reinterpret_cast<volatile int *>(ctrl_p + 864);
+  volatile int *uses = reinterpret_cast<volatile int *>(ctrl_p + 512);     // [PP][2G] completed phases of each inbox mbarrier
 
   // (divisions by multiplication: the host checks the ranges)
   const int cid = frag_div(blockIdx.x, a.inv_s);
@@ -340,12 +348,12 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
   if (S > 1) cluster_arrive_relaxed();  // the init fence above is what the peers need; nothing else to publish yet
 
   // This warp's tile sequence: its panels in order, in each its units wu + qi * Wu. The fetch
-  // cursor runs kFragRing - 1 tiles ahead of the compute cursor. Lane 0 issues the copies; every
+  // cursor runs R - 1 tiles ahead of the compute cursor. Lane 0 issues the copies; every
   // lane keeps the cursor.
-  const uint32_t wbar = ctrl + 512u + (uint32_t)warp * kFragRing * 8u;  // this warp's ring mbarriers
+  const uint32_t wbar = ctrl + 1024u + (uint32_t)warp * kFragMaxRing * 8u;  // this warp's ring mbarriers
   if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < kFragRing; ++i) mbar_init_u32(wbar + 8u * i, 1);
+    for (int i = 0; i < kFragMaxRing; ++i) mbar_init_u32(wbar + 8u * i, 1);
     mbar_fence_init();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copy engine sees the barriers initialised
   }
@@ -367,14 +375,13 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
       f_src += step_panel;
     }
     f_slot += kStride;
-    if (++f_idx == kFragRing) {
+    if (++f_idx == R) {
       f_idx = 0;
       f_slot = ring;
     }
   };
   // The weight tiles are written by no earlier kernel: their first copies go out at once.
-#pragma unroll
-  for (int i = 0; i < kFragRing - 1; ++i) fetch();
+  for (int i = 0; i < R - 1; ++i) fetch();
 
   // x may be the output of the kernel before this one and y may still be read by it: wait for the
   // earlier kernels (returns at once unless this kernel was launched early).
@@ -448,7 +455,7 @@ __global__ void __launch_bounds__(kFragMaxWarps * 32, 1) frag_kernel(const FragA
         ISHI_SPENT(17, c1, c2);
         uq += Wu;
         c_slot += kStride;
-        if (++c_idx == kFragRing) {
+        if (++c_idx == R) {
           c_idx = 0;
           c_slot = ring;
           c_phase ^= 1u;

@@ -192,13 +192,18 @@ class OutputExchange:
 
         self._check(self.lib.ishi_exchange_wait(self.handle, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
 
-    def close(self) -> None:
+    def close(self, barrier: bool = True) -> None:
+        """Disconnects from the peers, waits for every rank to have done so, then frees the buffer
+        (a peer's last launch may still be storing into it until then). All ranks call it."""
         if getattr(self, "handle", None):
+            self.lib.ishi_exchange_disconnect(self.handle)
+            if barrier and self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)
             self.lib.ishi_exchange_destroy(self.handle)
             self.handle = None
 
     def __del__(self):
         try:
-            self.close()
+            self.close(barrier=False)  # a finaliser cannot count on the other ranks
         except Exception:
             pass
