@@ -109,8 +109,10 @@ ishi_status ishi_ctx_set_route(ishi_ctx *ctx, int route, int crossover_rows);
 /* ---- projection: PackedLinear ------------------------------------------------------------- */
 
 /* PackedLinear.init + VerifyMatmul.warm (Hadamard.swift:51-86, VerifyMatmul.swift:40-61):
- * validates the weight, fixes the launch plan for its shape, allocates the projection's own
- * memory and copies the weight into it in tiled order (synchronises the device once). */
+ * validates the weight, allocates the projection's own memory, copies the weight into it in tiled
+ * order and fixes the launch plan for its shape: for the warp-level kernel's formats by timing the
+ * best few candidate plans on the tiled weight (about a millisecond; ISHI_NO_AUTOTUNE=1 in the
+ * environment keeps the estimate's choice). Synchronises the device. */
 ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc,
                                    ishi_projection **out);
 /* Several weights of one format and input width as ONE projection: their output rows stacked in

@@ -383,6 +383,13 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
   // The weight tiles are written by no earlier kernel: their first copies go out at once.
   for (int i = 0; i < R - 1; ++i) fetch();
 
+  // Warm L2 and the address translation with this CTA's slice of x. Only a hint: x may still be
+  // written by the kernel before this one, its values are read after the wait below, through L2.
+  for (int r = warp; r < a.M; r += (int)(blockDim.x >> 5)) {
+    const char *row = reinterpret_cast<const char *>(a.x + (long long)r * a.K + (long long)ub0 * 256);
+    for (int c = lane; c < uc * 4; c += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + c * 128));
+  }
+
   // x may be the output of the kernel before this one and y may still be read by it: wait for the
   // earlier kernels (returns at once unless this kernel was launched early).
   asm volatile("griddepcontrol.wait;" ::: "memory");
