@@ -133,6 +133,13 @@ int64_t ishi_projection_weight_bytes(const ishi_projection *p);
  * crossover_rows, or the built-in 1. The counterpart of VerifyMatmul.minimumRows(bytes:)
  * (VerifyMatmul.swift:19-26), whose table was tuned for Apple M1 (ishi_reference_minimum_rows). */
 int ishi_projection_crossover_rows(const ishi_projection *p);
+/* The launch plan create settled on, for the warp-level kernel's formats: {K split = cluster size,
+ * warps per panel, panels in parallel, tiles per warp ring} (zeros for the other kernels), and a way
+ * to impose one: the order in which partial sums are added follows the plan, so two projections of
+ * the same weight agree bit for bit only under the same plan (the tiled copy does not depend on
+ * it). set_plan accepts what ishi_projection_plan of a projection of the same shape returned. */
+ishi_status ishi_projection_plan(const ishi_projection *p, int plan[4]);
+ishi_status ishi_projection_set_plan(ishi_projection *p, const int plan[4]);
 
 /* PackedLinear.callAsFunction (Hadamard.swift:180-213): rotates x when the pack is rotated,
  * then multiplies. rows in 1...16. */

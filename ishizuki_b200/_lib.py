@@ -49,6 +49,8 @@ SIGNATURES = {
     "ishi_projection_output_dim": (c_int64, [c_void_p]),
     "ishi_projection_weight_bytes": (c_int64, [c_void_p]),
     "ishi_projection_crossover_rows": (c_int, [c_void_p]),
+    "ishi_projection_plan": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    "ishi_projection_set_plan": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
     "ishi_projection_apply": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p]),
     "ishi_projection_apply_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "ishi_projection_rotate": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),

@@ -1026,6 +1026,32 @@ int ishi_projection_crossover_rows(const ishi_projection *p) {
   return p->ctx->crossover_rows > 0 ? p->ctx->crossover_rows : 1;
 }
 
+ishi_status ishi_projection_plan(const ishi_projection *p, int plan[4]) {
+  if (!p || !plan) return ISHI_E_INVALID;
+  plan[0] = plan[1] = plan[2] = plan[3] = 0;
+  if (p->frag.ok) plan[0] = p->frag.S, plan[1] = p->frag.Wu, plan[2] = p->frag.PP, plan[3] = p->frag.ring;
+  return ISHI_OK;
+}
+
+ishi_status ishi_projection_set_plan(ishi_projection *p, const int plan[4]) {
+  if (!p || !plan) return ISHI_E_INVALID;
+  ishi_ctx *ctx = p->ctx;
+  if (!p->frag.ok) return fail(ctx, ISHI_E_UNSUPPORTED, "this projection's kernel has one launch plan only");
+  std::lock_guard<std::mutex> g(ctx->lock);
+  ishi_weight_desc d = p->d;
+  d.weight_dev = p->ws.tiles;  // the planner looks at sizes only
+  std::vector<FragPlan> all;
+  FragPlan best;
+  if (!make_frag_plan(ctx, d, &best, &all)) return fail(ctx, ISHI_E_SHAPE, "no launch plan fits");
+  for (const FragPlan &c : all)
+    if (c.S == plan[0] && c.Wu == plan[1] && c.PP == plan[2] && c.ring == plan[3]) {
+      p->frag = c;
+      return ISHI_OK;
+    }
+  return fail(ctx, ISHI_E_INVALID, "plan %d,%d,%d,%d is not among this projection's launch plans", plan[0], plan[1], plan[2],
+              plan[3]);
+}
+
 ishi_status ishi_projection_rotate(ishi_projection *p, const void *x, int rows, void *xr, void *stream) {
   if (!p) return ISHI_E_INVALID;
   ishi_ctx *ctx = p->ctx;

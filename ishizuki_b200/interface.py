@@ -328,6 +328,19 @@ class PackedLinear:
     def crossoverRows(self) -> int:  # noqa: N802
         return int(self.ctx.lib.ishi_projection_crossover_rows(self.handle))
 
+    @property
+    def plan(self) -> tuple[int, int, int, int]:
+        """The launch plan create settled on (K split, warps per panel, panels in parallel, ring);
+        zeros for a format outside the warp-level kernel."""
+        out = (ctypes.c_int * 4)()
+        self.ctx.check(self.ctx.lib.ishi_projection_plan(self.handle, out), declined=())
+        return tuple(int(v) for v in out)
+
+    def set_plan(self, plan) -> None:
+        """Imposes another projection's plan: partial sums are then added in the same order."""
+        arr = (ctypes.c_int * 4)(*[int(v) for v in plan])
+        self.ctx.check(self.ctx.lib.ishi_projection_set_plan(self.handle, arr), declined=())
+
     def _rows(self, x: torch.Tensor) -> tuple[torch.Tensor, tuple[int, ...]]:
         if x.dtype != torch.float16 or not x.is_cuda:
             raise TypeError("activations must be fp16 CUDA tensors")

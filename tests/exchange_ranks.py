@@ -43,8 +43,16 @@ def main() -> None:
         x = torch.from_numpy(synth.activations(rng, 8, k)).cuda()
         n_local = local.outputDim
         off, view = ex.reserve(n_local * world)
-        # what every rank's shard gives, computed here
-        want = torch.cat([build(q)(x, transposed=True) for q in range(world)])
+        # what every rank's shard gives, computed here under the launch plan its owner measured
+        # (the plan fixes the order of the partial sums, hence the bits)
+        plans = [None] * world
+        dist.all_gather_object(plans, local.plan)
+        pieces = []
+        for q in range(world):
+            ref = build(q)
+            ref.set_plan(plans[q])
+            pieces.append(ref(x, transposed=True))
+        want = torch.cat(pieces)
         cases.append((local, x, off, view, n_local, want))
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):

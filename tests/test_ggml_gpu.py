@@ -237,6 +237,23 @@ def test_stacked_affine_packs():
         assert rel_err(piece.cpu().numpy(), want32) < TOL
 
 
+def test_a_projection_under_another_ones_plan_gives_the_same_bits():
+    """create measures its launch plan; the plan fixes the order of the partial sums. A second
+    projection of the same weight agrees bit for bit once it is given the first one's plan."""
+    rng = np.random.default_rng(21)
+    n, k = 2048, 4096
+    blocks = dev(synth.q4k_blocks(rng, n, k))
+    a = PackedLinear(ggml=GGUFBlocks(blocks, GGMLType.q4K, (n, k)))
+    b = PackedLinear(ggml=GGUFBlocks(blocks, GGMLType.q4K, (n, k)))
+    assert all(v > 0 for v in a.plan)
+    x = dev(synth.activations(rng, 8, k))
+    b.set_plan(a.plan)
+    assert b.plan == a.plan
+    assert torch.equal(a(x), b(x))
+    with pytest.raises(IshizukiError):
+        b.set_plan((2, 25, 8, 3))  # more warps than a block holds: not a plan of this projection
+
+
 def test_stacking_guards():
     rng = np.random.default_rng(2)
     a = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 512)), GGMLType.q4K, (32, 512))
