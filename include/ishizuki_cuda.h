@@ -267,7 +267,8 @@ ishi_status ishi_q4k_matmul_few_static(const void *x_dev, int rows, const void *
  *
  * An exchange owns, on every rank, one buffer of out_bytes for outputs and a few arrival words.
  * Outputs are fp16 arrays [rows of all shards][8]: row n holds the (up to 8) drafted rows'
- * values of output n, the transposed form of ishi_projection_apply. All ranks must issue the same
+ * values of output n, the transposed form of ishi_projection_apply; a call with 9...16 drafted
+ * rows uses [rows of all shards][16] instead (two launches). All ranks must issue the same
  * sequence of ishi_exchange_apply calls. Waits on the device are bounded (about a second) and
  * raise the context's error word (ishi_ctx_poll) instead of hanging. */
 typedef struct ishi_exchange ishi_exchange;
@@ -282,8 +283,9 @@ ishi_status ishi_exchange_export(ishi_exchange *ex, void *handle_out);
 ishi_status ishi_exchange_connect(ishi_exchange *ex, const void *handles);
 /* This rank's output buffer (device pointer). */
 void *ishi_exchange_buffer(ishi_exchange *ex);
-/* x [rows, k] (rows 1...8) against this rank's shard; the rows land at
- * buffer + out_offset_bytes, rows [row_offset, row_offset + n) of the [.][8] array, on every rank.
+/* x [rows, k] (rows 1...16) against this rank's shard; the rows land at
+ * buffer + out_offset_bytes, rows [row_offset, row_offset + n) of the [.][8] array ([.][16] when
+ * rows > 8), on every rank.
  * wait_previous != 0: the kernel first waits until every rank's previous ishi_exchange_apply has
  * landed here (use it when x was produced from exchanged outputs). */
 ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const void *x_dev, int rows,

@@ -571,8 +571,9 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     if (peers) {
       a.world = peers->world;
       a.rank = peers->rank;
+      a.peer_ld = rows > 8 ? 16 : 8;  // the second piece of eight rows lies beside the first
       for (int q = 0; q < peers->world; ++q) {
-        a.peer_y[q] = peers->y[q];
+        a.peer_y[q] = peers->y[q] + r0;
         a.peer_flags[q] = peers->flags[q];
       }
       a.local_flags = peers->local_flags;
@@ -1331,11 +1332,47 @@ ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const voi
   ishi_ctx *ctx = ex->ctx;
   if (p->ctx != ctx) return fail(ctx, ISHI_E_INVALID, "projection and exchange belong to different contexts");
   if (!ex->connected) return fail(ctx, ISHI_E_INVALID, "exchange not connected");
-  if (!p->frag.ok) return fail(ctx, ISHI_E_UNSUPPORTED, "this weight format has no kernel with an output exchange");
   if (!x) return fail(ctx, ISHI_E_INVALID, "null pointer");
-  if (rows < 1 || rows > 8) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...8", rows);
+  if (!p->frag.ok) {
+    // The other kernels do not store to peers themselves: the product goes into this rank's own
+    // copy and a small kernel passes the rows on and publishes them.
+    if (rows < 1 || rows > 8) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...8 for this weight format", rows);
+    if (p->d.hadamard_block != 0) return fail(ctx, ISHI_E_UNSUPPORTED, "a rotated pack of this format cannot be exchanged");
+    if (out_offset_bytes < 0 || (out_offset_bytes & 15) || row_offset < 0 ||
+        (size_t)out_offset_bytes + (size_t)(row_offset + p->d.n) * 16 > ex->bytes)
+      return fail(ctx, ISHI_E_SHAPE, "rows %lld...%lld at offset %lld do not fit the exchange buffer", (long long)row_offset,
+                  (long long)(row_offset + p->d.n), (long long)out_offset_bytes);
+    ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (wait_previous) {
+      peer_wait_kernel<<<1, 32, 0, st>>>(ex->words, ex->world, ex->words + 17, ctx->err_dev);
+      ISHI_CUDA(ctx, cudaGetLastError());
+    }
+    __half *mine = reinterpret_cast<__half *>(ex->buf + out_offset_bytes);
+    ishi_status s = projection_matmul(p, x, rows, mine + row_offset * 8, 8, ISHI_OUT_TRANSPOSED, false, st);
+    if (s != ISHI_OK) return s;
+    PublishArgs pa;
+    memset(&pa, 0, sizeof(pa));
+    for (int q = 0; q < ex->world; ++q) {
+      pa.peer_y[q] = reinterpret_cast<__half *>(ex->peer_buf[q] + out_offset_bytes);
+      pa.peer_flags[q] = ex->peer_words[q];
+    }
+    pa.done = ex->words + 16;
+    pa.launch_no = ex->words + 17;
+    pa.first = row_offset;
+    pa.n = p->d.n;
+    pa.world = ex->world;
+    pa.rank = ex->rank;
+    pa.M = rows;
+    const int grid = (int)std::min<long long>((p->d.n + 255) / 256, ctx->sm_count);
+    publish_rows_kernel<<<grid, 256, 0, st>>>(pa);
+    ISHI_CUDA(ctx, cudaGetLastError());
+    return ISHI_OK;
+  }
+  if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  const size_t row_bytes = rows > 8 ? 32 : 16;
   if (out_offset_bytes < 0 || (out_offset_bytes & 15) || row_offset < 0 ||
-      (size_t)out_offset_bytes + (size_t)(row_offset + p->d.n) * 16 > ex->bytes)
+      (size_t)out_offset_bytes + (size_t)(row_offset + p->d.n) * row_bytes > ex->bytes)
     return fail(ctx, ISHI_E_SHAPE, "rows %lld...%lld at offset %lld do not fit the exchange buffer", (long long)row_offset,
                 (long long)(row_offset + p->d.n), (long long)out_offset_bytes);
   const int b = p->d.hadamard_block;
@@ -1354,7 +1391,7 @@ ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const voi
   po.launch_no = ex->words + 17;
   po.wait_previous = wait_previous ? 1 : 0;
   po.row_offset = row_offset;
-  return run_frag(ctx, p->frag, p->ws, p->d, x, rows, ex->buf + out_offset_bytes, 8, ISHI_OUT_TRANSPOSED, false,
+  return run_frag(ctx, p->frag, p->ws, p->d, x, rows, ex->buf + out_offset_bytes, rows > 8 ? 16 : 8, ISHI_OUT_TRANSPOSED, false,
                   getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, b != 0, static_cast<cudaStream_t>(stream), &po);
 }
 

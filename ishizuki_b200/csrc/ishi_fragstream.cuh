@@ -75,11 +75,12 @@ struct FragArgs {
   int rot_block;           // a power of two, 8 ... 256
   const float *rot_signs;  // [K] or null
   // Output exchange between the GPUs of an N-sharded projection (world = 0: none). Every rank holds
-  // the whole output as [rows of all shards][8] fp16 at the same place of its exchange buffer; this
+  // the whole output as [rows of all shards][8 or 16] fp16 at the same place of its exchange buffer; this
   // launch computes rows row_offset ... row_offset + N - 1 and stores them into every rank's copy
   // over NVLink. When all CTAs have stored, the rank writes seq into its arrival word on every rank.
   int world, rank;
   __half *peer_y[kFragMaxPeers];          // the output array in every rank's buffer ([rank]: the local one)
+  int peer_ld;                            // fp16 values between its rows: 8, or 16 when the call has more than 8 rows
   unsigned *peer_flags[kFragMaxPeers];    // every rank's arrival words; this rank writes word [rank] of each
   unsigned *local_flags;                  // this rank's arrival words, one per rank
   unsigned *done;                         // CTAs of this launch that have stored their rows
@@ -217,7 +218,7 @@ __device__ __forceinline__ void frag_write(const FragArgs &a, int p, int lane, f
     const long long n = n0 + ((t & 2) ? 8 : 0);
     if (n < a.N) {
       const uint4 row = (t & 2) ? rhi : rlo;
-      for (int q = t & 1; q < a.world; q += 2) *reinterpret_cast<uint4 *>(a.peer_y[q] + (a.row_offset + n) * 8) = row;
+      for (int q = t & 1; q < a.world; q += 2) *reinterpret_cast<uint4 *>(a.peer_y[q] + (a.row_offset + n) * a.peer_ld) = row;
     }
     return;
   }
@@ -612,6 +613,44 @@ static __global__ void peer_wait_kernel(const unsigned *local_flags, int world, 
       if (!ok) __nanosleep(64);
     }
     if (!ok) *err = 2;
+  }
+}
+
+// The exchange for products of the other kernels: rows [first, first + n) of this rank's own
+// [.][8] array (just written by the product) go to every other rank's copy, columns past M
+// cleared; then the same publication as in frag_kernel (last CTA: one system-scope fence, the
+// launch number into this rank's arrival word on every rank).
+struct PublishArgs {
+  __half *peer_y[kFragMaxPeers];
+  unsigned *peer_flags[kFragMaxPeers];
+  unsigned *done, *launch_no;
+  long long first, n;
+  int world, rank, M;
+};
+static __global__ void __launch_bounds__(256) publish_rows_kernel(const PublishArgs a) {
+  const unsigned previous_launch = *reinterpret_cast<volatile unsigned *>(a.launch_no);
+  uint4 *mine = reinterpret_cast<uint4 *>(a.peer_y[a.rank]) + a.first;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (long long)gridDim.x * blockDim.x) {
+    uint4 v = mine[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (2 * j >= a.M) w[j] = 0u;
+      else if (2 * j + 1 >= a.M) w[j] &= 0xffffu;
+    }
+    v = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int q = 0; q < a.world; ++q) (reinterpret_cast<uint4 *>(a.peer_y[q]) + a.first)[i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned before = atomicAdd(a.done, 1u);
+    if (before == gridDim.x - 1) {
+      *reinterpret_cast<volatile unsigned *>(a.done) = 0u;
+      *reinterpret_cast<volatile unsigned *>(a.launch_no) = previous_launch + 1u;
+      __threadfence_system();
+      for (int q = 0; q < a.world; ++q) st_relaxed_sys(a.peer_flags[q] + a.rank, previous_launch + 1u);
+    }
   }
 }
 

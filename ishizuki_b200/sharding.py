@@ -168,17 +168,20 @@ class OutputExchange:
         if rc != 0:
             raise self._err(rc, self.ctx.last_error())
 
-    def reserve(self, n_total: int) -> tuple[int, torch.Tensor]:
-        """Room for one output [n_total, 8] fp16: its byte offset and a view of the local copy."""
+    def reserve(self, n_total: int, rows: int = 8) -> tuple[int, torch.Tensor]:
+        """Room for one output [n_total, 8] fp16 ([n_total, 16] for calls with more than 8 drafted
+        rows): its byte offset and a view of the local copy."""
+        width = 16 if rows > 8 else 8
         off = self.used
-        size = n_total * 16
+        size = n_total * width * 2
         if off + size > self.nbytes:
             raise ValueError(f"exchange buffer of {self.nbytes} bytes is full")
         self.used = off + ((size + 255) & ~255)
-        return off, self.buffer[off: off + size].view(torch.float16).view(n_total, 8)
+        return off, self.buffer[off: off + size].view(torch.float16).view(n_total, width)
 
     def apply(self, local, x: torch.Tensor, offset: int, row_offset: int, wait_previous: bool = True) -> None:
-        """local: interface.PackedLinear over this rank's rows; x [rows <= 8, K] fp16 on this GPU."""
+        """local: interface.PackedLinear over this rank's rows; x [rows <= 16, K] fp16 on this GPU
+        (more than 8 rows need an output reserved with rows > 8)."""
         import ctypes
 
         rows = x.shape[0]

@@ -30,11 +30,14 @@ def _projection(fmt, rng, n, k):
         return PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
     if fmt == "q6_k":
         return PackedLinear(ggml=GGUFBlocks(dev(synth.q6k_blocks(rng, n, k)), GGMLType.q6K, (n, k)))
+    if fmt in ("iq2_xs", "iq4_xs"):  # the tcgen05 kernel / the one-warp-per-row kernel: product, then a publishing kernel
+        type_id = GGMLType.iq2Xs if fmt == "iq2_xs" else GGMLType.iq4Xs
+        return PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k)))
     w, s, b = synth.affine_pack(rng, n, k, 4, 64, np.float16)
     return PackedLinear(dev(w), dev(s), dev(b), None, 0, groupSize=64, bits=4)
 
 
-@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "affine4"])
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "affine4", "iq2_xs", "iq4_xs"])
 @pytest.mark.parametrize("rows", [1, 5, 8])
 def test_single_rank_exchange_matches_projection(rows, fmt):
     rng = np.random.default_rng(rows)
@@ -54,6 +57,26 @@ def test_single_rank_exchange_matches_projection(rows, fmt):
     assert torch.equal(view_a[:, :rows], want)
     assert torch.equal(view_b[:, :rows], want)
     assert not view_a[:, rows:].any()
+    ex.close()
+
+
+def test_single_rank_exchange_of_thirteen_rows():
+    """More than eight drafted rows: two launches, the pieces side by side in a [N, 16] array."""
+    rng = np.random.default_rng(13)
+    n, k, rows = 1000, 2048, 13
+    lin = _projection("q4_k", rng, n, k)
+    ex = OutputExchange(1 << 20)
+    off, view = ex.reserve(n, rows)
+    x = dev(synth.activations(rng, rows, k))
+    want = lin(x, transposed=True)
+    for _ in range(2):
+        ex.apply(lin, x, off, 0)
+    ex.wait()
+    torch.cuda.synchronize()
+    lin.ctx.poll()
+    assert view.shape == (n, 16)
+    assert torch.equal(view[:, :rows], want)
+    assert not view[:, rows:].any()
     ex.close()
 
 
