@@ -41,6 +41,7 @@ struct FragAffine {
   static constexpr int kRowHeader = 4 * kGroups;     // bytes per row there
   static constexpr int kTileBytes = kHeader + 16 * kRowHeader;
   static constexpr int kSums = 4096;                 // offset of the group sums of x: [group][activation row] fp32
+  static constexpr int kExtraBytes = 0;  // shared memory per CTA beyond the per-unit staging
   static constexpr bool kRowMode = true;  // MODE 1: one activation row on CUDA cores
   static constexpr int kXBytes = 4096 + (32 * kGroups > 128 ? 32 * kGroups : 128);
 

@@ -41,6 +41,7 @@ namespace ishi {
 
 struct FragQ4K {
   static constexpr int kTileBytes = 16 * 144;
+  static constexpr int kExtraBytes = 0;  // shared memory per CTA beyond the per-unit staging
   static constexpr bool kRowMode = true;  // MODE 1: one activation row on CUDA cores
   static constexpr int kSumBytes = 384;  // per unit: sub-block sums as fp16 hi / lo pairs, [lane][8 bytes], then
                                          // the fp32 sub-block sums of row 0 (single-row kernel) @256

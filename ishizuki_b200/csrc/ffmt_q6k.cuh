@@ -40,6 +40,7 @@ struct FragQ6K {
   static constexpr int kTileBytes = 16 * 210;
   static constexpr int kXSums = 4096;             // after the activations: [lane][hi hi | lo lo] group sums
   static constexpr int kXBytes = kXSums + 512;    // per unit
+  static constexpr int kExtraBytes = 0;  // shared memory per CTA beyond the per-unit staging
   static constexpr bool kRowMode = false;         // one activation row runs through the MMA path as well
 
   // the 6-bit code of weight k of a block

@@ -23,6 +23,7 @@ namespace ishi {
 // the per-format kernel tables (frag_*.cu, row_*.cu)
 const FragOps *frag_ops_q4k();
 const FragOps *frag_ops_q6k();
+const FragOps *frag_ops_iq2xs();
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
 const FragOps *frag_ops_affine2(int group_size, bool bf16);
 const RowOps *row_ops_ggml(int type);
@@ -377,11 +378,13 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
 
 // ---- warp-level kernel: plan, tiling, launch ------------------------------------------------------
 
-// The fragment decoder that serves a weight, or null (the tcgen05 kernel then takes it).
+// The fragment decoder that serves a weight, or null (the tcgen05 kernel then takes it, as it does
+// when no plan of the warp-level kernel fits shared memory: very wide inputs).
 const FragOps *frag_ops_for(const ishi_weight_desc &d) {
   if (d.kind == ISHI_KIND_GGML) {
     if (d.ggml_type == ISHI_GGML_Q4_K) return frag_ops_q4k();
     if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
+    if (d.ggml_type == ISHI_GGML_IQ2_XS) return frag_ops_iq2xs();
     return nullptr;
   }
   if (d.scale_dtype != ISHI_DT_F16 && d.scale_dtype != ISHI_DT_BF16) return nullptr;
@@ -426,8 +429,11 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl, std:
     if (fs && s != fs) continue;
     const int umax = (units + s - 1) / s;
     const int per_min = (umax + kFragMaxWarps - 1) / kFragMaxWarps;
-    for (int per = per_min; per <= std::min(per_min + 2, kFragGroup); ++per) {
-      if (fper && per != fper) continue;
+    // units per warp: a few around the fewest that fit the warps, and the whole range and half of
+    // it in one warp (no or little adding up between the warps of a panel)
+    const int per_hi = std::min(per_min + 2, kFragGroup);
+    for (int per = per_min; per <= umax; ++per) {
+      if (fper ? per != fper : (per > per_hi && per != umax && per != (umax + 1) / 2)) continue;
       const int wu = (umax + per - 1) / per;
       for (int pp = 1; pp <= kFragMaxPanels && wu * pp <= kFragMaxWarps; ++pp) {
         if (fpp && pp != fpp) continue;
@@ -445,7 +451,7 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl, std:
         bool fits = false;
         for (int ring = fring ? fring : 3; ring >= (fring ? fring : 2) && !fits; --ring)
           for (int gen = 2; gen >= 1 && !fits; --gen) {
-            const size_t need = frag_smem_bytes(umax, xbytes, w, pp, gen, s, tile_bytes, ring);
+            const size_t need = frag_smem_bytes((size_t)umax * xbytes + ops->x_extra, w, pp, gen, s, tile_bytes, ring);
             if (need <= budget) {
               fits = true;
               c.ring = ring, c.G = gen, c.smem = need;

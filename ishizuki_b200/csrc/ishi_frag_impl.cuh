@@ -76,7 +76,7 @@ struct FragOpsOf {
   }
 
   static constexpr FragOps ops() {
-    return FragOps{Fmt::kTileBytes, Fmt::kXBytes, &configure, &max_clusters, &launch, &prepare};
+    return FragOps{Fmt::kTileBytes, Fmt::kXBytes, Fmt::kExtraBytes, &configure, &max_clusters, &launch, &prepare};
   }
 };
 

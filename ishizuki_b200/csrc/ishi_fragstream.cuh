@@ -182,9 +182,9 @@ __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_b
 // control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @768, done [PP] @832,
 // abort @864, phases used of every inbox mbarrier [PP][2G] @512, ring mbarriers [warp][kFragMaxRing] @1024
 constexpr uint32_t kFragCtrlBytes = 2048;
-__host__ __device__ inline size_t frag_smem_bytes(int umax, int xbytes, int W, int PP, int G, int S, int tile_bytes,
-                                                  int ring) {
-  return (size_t)umax * xbytes + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
+// xregion: the format's activation staging, umax * Fmt::kXBytes + Fmt::kExtraBytes
+__host__ __device__ inline size_t frag_smem_bytes(size_t xregion, int W, int PP, int G, int S, int tile_bytes, int ring) {
+  return xregion + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
          (size_t)W * ring * frag_ring_stride(tile_bytes);
 }
 
@@ -304,8 +304,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
   // scheduler's preference for its oldest warps then cannot starve a whole lane.
   const int wu = frag_div((unsigned)warp, a.inv_pp), wp = warp - wu * PP;
 
-  const uint32_t xfrag = smem_u32(smem);                                   // [umax][Fmt::kXBytes]
-  const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes;            // [PP][kFragRed][Wu][128 floats]
+  const uint32_t xfrag = smem_u32(smem);                                   // [umax][Fmt::kXBytes], then Fmt::kExtraBytes
+  const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes + Fmt::kExtraBytes;  // [PP][kFragRed][Wu][128 floats]
   const uint32_t inbox = red + (uint32_t)(W * kFragRed) * 512u;            // [PP][2G][S][128 floats]
   const uint32_t ctrl = inbox + (S > 1 ? (uint32_t)(PP * 2 * G * S) * 512u : 0u);
   const int R = a.ring;  // tiles in this warp's ring

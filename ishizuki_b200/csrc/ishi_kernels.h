@@ -20,7 +20,7 @@ struct FragLaunch {
 };
 
 struct FragOps {
-  int tile_bytes, x_bytes;
+  int tile_bytes, x_bytes, x_extra;  // bytes per tile; activation staging per unit of the column range, and per CTA
   // raises the dynamic shared memory limit of every variant (once per device)
   cudaError_t (*configure)(int max_smem);
   // how many clusters of `split` CTAs the device keeps resident, 0 if the launch is impossible
