@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Benchmark of the speculative-verify quantized matmul.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload stack|mlp] [--layers L] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload stack|mlp|formats] [--layers L] [--impl ours|reference]
 
 Workload (default, at every N): the verify stack of a 27B model in GGUF Q4_K, 64 layers of
 q / k / v / o / gate / up / down projections (q 6144x5120, k and v 1024x5120, o 5120x6144, gate and
@@ -9,7 +9,9 @@ up 17408x5120, down 5120x17408) against M = 8 drafted rows of fp16 activations, 
 fp16 outputs. Projections that read the same input are stacked into one launch (q+k+v, gate+up), so
 a layer is four launches; every projection has its own weights (12.27 GB per pass, far more than
 L2) and its own fresh N(0,1) activations. `--workload mlp` runs gate/up/down only (the 1-GPU MLP
-configuration). Inputs are synthetic with the configured value distributions, drawn on the GPU
+configuration), `--workload formats` only the per-format side table (every weight format on the
+gate shape at M = 1 and M = 8, the 4096 x 4096 affine projection, a ternary layer; ISHI_BENCH_FORMATS
+and ISHI_BENCH_ROWS narrow it for profiler captures). Inputs are synthetic with the configured value distributions, drawn on the GPU
 from seeded generators: real GGUF files are not available where this runs.
 
 The metric is weight GB/s: compressed weight bytes streamed per second (GB = 1e9), the
@@ -322,7 +324,7 @@ def format_table(peak: float) -> dict:
     import torch
 
     from ishizuki_b200 import _lib, synth
-    from ishizuki_b200.interface import BonsaiRuntime, GGMLType, GGUFBlocks, PackedLinear
+    from ishizuki_b200.interface import BonsaiRuntime, FusedLinear, GGMLType, GGUFBlocks, PackedLinear
 
     def dev(a):
         return torch.from_numpy(np.ascontiguousarray(a)).cuda()
@@ -395,10 +397,18 @@ def format_table(peak: float) -> dict:
     table["affine4_g64_4096x4096"] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, 4096),
                                       "m8": measure(lins, 8, 4096)}
     del lins
-    # configuration 4: the seven ternary projections of a layer, per layer
-    shapes = [(6144, 5120), (1024, 5120), (1024, 5120), (5120, 6144), (17408, 5120), (17408, 5120), (5120, 17408)]
-    layers = [[make("ternary", n_, k_) for n_, k_ in shapes] for _ in range(3)]
-    row = {"weight_mb": sum(lin.weightBytes for lin in layers[0]) / 1e6}
+    # configuration 4: the seven ternary projections of a layer, per layer; as in the headline
+    # stack, projections that read the same input are one stacked launch (q+k+v, gate+up)
+    def ternary_group(k_, sizes):
+        packs = [synth.ternary_pack(rng, n_, k_, 128) for n_ in sizes]
+        parts = [(dev(w), dev(sb).view(torch.bfloat16), dev(bb).view(torch.bfloat16)) for w, sb, bb in packs]
+        if len(parts) == 1:
+            return PackedLinear(parts[0][0], parts[0][1], parts[0][2], None, 128, groupSize=128, bits=2)
+        return FusedLinear(parts, None, 128, groupSize=128, bits=2)
+
+    groups4 = [(5120, (6144, 1024, 1024)), (6144, (5120,)), (5120, (17408, 17408)), (17408, (5120,))]
+    layers = [[ternary_group(k_, sizes) for k_, sizes in groups4] for _ in range(3)]
+    row = {"weight_mb": sum(lin.weightBytes for lin in layers[0]) / 1e6, "launches_per_layer": len(groups4)}
     for m in (1, 8):
         xs = {k_: dev(synth.activations(rng, m, k_)) for k_ in (5120, 6144, 17408)}
         outs = [[torch.empty((m, lin.outputDim), dtype=torch.float16, device="cuda") for lin in layer] for layer in layers]

@@ -8,7 +8,10 @@
 //   nibble: the second sixteen);  w = d * (2 s + 1) / 8 * magnitude * sign.
 //
 // Decode: the grid lives in shared memory as fp16 (512 entries x 16 bytes = one 16-byte load per
-// eight weights = four A registers); a register then takes its scale by a half2 multiply with
+// eight weights = four A registers), in eight copies, copy c of entry i at i * 128 + c * 16: a
+// 16-byte load is served eight lanes at a time, lane l reads copy l % 8, so the eight lanes of a
+// pass always hit eight different bank groups whatever their indices are (one copy alone measured
+// 2.2 million bank conflicts per launch and warps stalled on shared memory 3.7 cycles per issue); a register then takes its scale by a half2 multiply with
 // 2 s + 1 (magnitude * (2 s + 1) <= 1333 is an exact fp16 integer) and its two signs by an
 // integer multiply that moves sign bits 2r and 2r + 1 to bits 15 and 31, xor-ed in. With the scale
 // inside the fragments a whole tile accumulates in one MMA chain; d / 8 remains for fp32.
@@ -37,7 +40,7 @@ struct FragIQ2XS {
   static constexpr int kTileBytes = 16 * 74;
   static constexpr int kXBytes = 8 * 512;        // per unit: eight rows of 512 bytes
   static constexpr int kGrid = 8 * 16;           // first in the extra region: the rows' 16-byte skews
-  static constexpr int kExtraBytes = kGrid + 512 * 16;  // then the grid as fp16
+  static constexpr int kExtraBytes = kGrid + 512 * 128;  // then the grid as fp16, eight copies interleaved
   static constexpr bool kRowMode = false;        // one activation row runs through the MMA path as well
 
   static __device__ __forceinline__ const uint8_t *block(const FragSrc &s, long long row, int u) {
@@ -88,7 +91,7 @@ struct FragIQ2XS {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const uint32_t R = row_stride(a);
     const int tasks = uc * 8;
-    constexpr int kBatch = 4;
+    constexpr int kBatch = 8;
     const __half *xl = a.x + (long long)ub0 * 256 + lane * 8;
     if (warp >= tasks) after_loads();  // a warp without a task
     for (int i0 = warp; i0 < tasks; i0 += nw * kBatch) {
@@ -120,7 +123,8 @@ struct FragIQ2XS {
         const uint32_t h1 = c1 == 0 ? 0x4800u : c1 == 1 ? 0x4e40u : 0x5160u;
         w[r] = h0 | (h1 << 16);
       }
-      sts128u(grid + (uint32_t)i * 16u, make_uint4(w[0], w[1], w[2], w[3]));
+#pragma unroll
+      for (int c = 0; c < 8; ++c) sts128u(grid + (uint32_t)i * 128u + (uint32_t)c * 16u, make_uint4(w[0], w[1], w[2], w[3]));
     }
   }
 
@@ -132,7 +136,7 @@ struct FragIQ2XS {
 
   // the eight weights of one u16 as four A registers: magnitude * (2 s + 1) * sign
   static __device__ __forceinline__ void entry(uint32_t (&r)[4], uint32_t q, uint32_t grid, __half2 scale) {
-    const uint4 m = lds128(grid + (q & 511u) * 16u);
+    const uint4 m = lds128(grid + (q & 511u) * 128u);  // grid: this lane's copy
     const uint32_t s7 = (q >> 9) & 127u;
     const uint32_t s8 = s7 | ((uint32_t)(__popc(s7) & 1) << 7);
     const uint32_t mag[4] = {m.x, m.y, m.z, m.w};
@@ -150,7 +154,7 @@ struct FragIQ2XS {
   static __device__ __forceinline__ void unit(float (&acc)[4], const FragArgs &a, uint32_t tile, uint32_t xbase, int uq,
                                               int g, int t, int lane) {
     const uint32_t R = row_stride(a);
-    const uint32_t grid = xbase + (uint32_t)a.umax * kXBytes + kGrid;
+    const uint32_t grid = xbase + (uint32_t)a.umax * kXBytes + kGrid + (uint32_t)(lane & 7) * 16u;
     const uint32_t xrow = xbase + (uint32_t)g * R + (uint32_t)uq * 512u + (uint32_t)t * 32u;
     const uint32_t sn = lds32(tile + 1024u + (uint32_t)lane * 4u);  // scale nibbles: row g low half, row g + 8 high half
     float c[4] = {0.f, 0.f, 0.f, 0.f};

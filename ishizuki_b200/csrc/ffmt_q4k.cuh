@@ -27,9 +27,11 @@
 // the word shifted by eight bits that of slots (2t + 8, 2t + 9), both in natural k order: the
 // activations are used as they lie in memory.
 //
-// Tile (16 rows x 256 k, 2304 bytes): piece jj = [lane][row g: 8 bytes, row g + 8: 8 bytes] for
-// jj = 0..3, then sixteen 16-byte row headers: d, dmin, and per t three bytes
-// sc[2t] | sc[2t+1] << 6 | m[2t] << 12 | m[2t+1] << 18. Same 144 bytes per block, regrouped.
+// Tile (16 rows x 256 k, 2368 bytes): piece jj = [lane][row g: 8 bytes, row g + 8: 8 bytes] for
+// jj = 0..3; then per row and t one word with the bytes m[2t], sc[2t], m[2t+1], sc[2t+1] (the
+// six-bit fields of the block's twelve packed bytes, one per byte: a lane's scales and minima then
+// come out with one byte permute or mask each; 64 bytes more than the 2304 of the blocks); then d
+// and dmin of every row.
 //
 // Activations of a unit in shared memory: eight rows of 256 fp16 as they lie in x, 576 bytes
 // apart (rows g and g + 1 then sit 64 bytes apart modulo the 128 bytes of a bank sweep), copied by
@@ -40,7 +42,7 @@
 namespace ishi {
 
 struct FragQ4K {
-  static constexpr int kTileBytes = 16 * 144;
+  static constexpr int kTileBytes = 2048 + 16 * 16 + 16 * 4;
   static constexpr int kExtraBytes = 0;  // shared memory per CTA beyond the per-unit staging
   static constexpr bool kRowMode = true;  // MODE 1: one activation row on CUDA cores
   static constexpr int kSumBytes = 384;  // per unit: sub-block sums as fp16 hi / lo pairs, [lane][8 bytes], then
@@ -72,19 +74,23 @@ struct FragQ4K {
       const int seg = frag_segment(s, row, &local);
       return s.w[seg][local * s.w_row_bytes + (long long)u * 144 + 16 + 32 * t + 8 * j + 4 * word + k];
     }
-    const int idx = b - 2048, off = idx & 15;
-    const long long row = p * kFragRows + (idx >> 4);
+    const int idx = b - 2048;
+    if (idx < 256) {
+      const long long row = p * kFragRows + (idx >> 4);
+      if (row >= s.N) return 0;
+      long long local;
+      const int seg = frag_segment(s, row, &local);
+      const uint8_t *blk = s.w[seg] + local * s.w_row_bytes + (long long)u * 144;
+      const int t = (idx >> 2) & 3, byte = idx & 3;
+      uint32_t sc, m;
+      scale_min(blk + 4, 2 * t + (byte >> 1), &sc, &m);
+      return (uint8_t)((byte & 1) ? sc : m);
+    }
+    const long long row = p * kFragRows + ((idx - 256) >> 2);
     if (row >= s.N) return 0;
     long long local;
     const int seg = frag_segment(s, row, &local);
-    const uint8_t *blk = s.w[seg] + local * s.w_row_bytes + (long long)u * 144;
-    if (off < 4) return blk[off];
-    const int t = (off - 4) / 3, byte = (off - 4) % 3;
-    uint32_t sa, ma, sb, mb;
-    scale_min(blk + 4, 2 * t, &sa, &ma);
-    scale_min(blk + 4, 2 * t + 1, &sb, &mb);
-    const uint32_t v = sa | (sb << 6) | (ma << 12) | (mb << 18);
-    return (uint8_t)(v >> (8 * byte));
+    return s.w[seg][local * s.w_row_bytes + (long long)u * 144 + (idx & 3)];
   }
 
   static __device__ __forceinline__ uint16_t tile_halfword(const FragSrc &s, long long p, int u, int hw) {
@@ -102,7 +108,7 @@ struct FragQ4K {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const uint32_t R = row_stride(a), sums = xfrag + 8u * R;
     const int tasks = uc * 8, jj = lane >> 3;
-    constexpr int kBatch = 4;
+    constexpr int kBatch = 8;
     const __half *xl = a.x + (long long)ub0 * 256 + lane * 8;
     if (warp >= tasks) after_loads();  // a warp without a task
     for (int i0 = warp; i0 < tasks; i0 += nw * kBatch) {
@@ -147,26 +153,19 @@ struct FragQ4K {
   static __device__ __forceinline__ float half_lo(uint32_t pair) { return __half2float(__ushort_as_half((unsigned short)(pair & 0xffffu))); }
   static __device__ __forceinline__ float half_hi(uint32_t pair) { return __half2float(__ushort_as_half((unsigned short)(pair >> 16))); }
 
-  // this lane's three scale bytes of a row header {h.x = d | dmin << 16, then twelve bytes}: bytes 3t ... 3t + 2 of them
-  static __device__ __forceinline__ uint32_t lane_group(const uint4 &h, int t) {
-    const uint32_t lo = t < 2 ? h.y : (t == 2 ? h.z : h.w);
-    const uint32_t hi = t == 1 ? h.z : h.w;
-    const uint32_t sh = t == 0 ? 0u : (t == 1 ? 24u : (t == 2 ? 16u : 8u));
-    return __funnelshift_r(lo, hi, sh) & 0xffffffu;
-  }
-
   // One tile against the activations of its unit. acc: the warp's C fragment (MODE 0) or this
   // lane's partial dot products of rows g (acc[0]) and g + 8 (acc[2]) (MODE 1).
   template <int MODE>
   static __device__ __forceinline__ void unit(float (&acc)[4], const FragArgs &a, uint32_t tile, uint32_t xbase, int uq,
                                               int g, int t, int lane) {
-    const uint4 h0 = lds128(tile + 2048u + (uint32_t)g * 16u), h1 = lds128(tile + 2048u + (uint32_t)(g + 8) * 16u);
-    const uint32_t v0 = lane_group(h0, t), v1 = lane_group(h1, t);
+    // this lane's sub-blocks 2t, 2t + 1 of rows g and g + 8: bytes m_lo, sc_lo, m_hi, sc_hi
+    const uint32_t v0 = lds32(tile + 2048u + (uint32_t)lane * 4u), v1 = lds32(tile + 2048u + 128u + (uint32_t)lane * 4u);
+    const uint32_t dd0 = lds32(tile + 2304u + (uint32_t)g * 4u), dd1 = lds32(tile + 2304u + 32u + (uint32_t)g * 4u);
     // low sub-block: the scale as an integer; high sub-block: sc / 16 as a half2 pair (the bits of
     // 64 + sc / 16, minus 64), so that both products come out in units of 2^-24
-    const uint32_t sl0 = v0 & 63u, sl1 = v1 & 63u;
+    const uint32_t sl0 = prmt(v0, 0u, 0x4441u), sl1 = prmt(v1, 0u, 0x4441u);
     const __half2 k64 = __float2half2_rn(64.f);
-    const uint32_t sh0p = ((v0 >> 6) & 63u) * 0x00010001u + 0x54005400u, sh1p = ((v1 >> 6) & 63u) * 0x00010001u + 0x54005400u;
+    const uint32_t sh0p = prmt(v0, 0x54545454u, 0x4343u), sh1p = prmt(v1, 0x54545454u, 0x4343u);
     const __half2 sh0 = __hsub2(*reinterpret_cast<const __half2 *>(&sh0p), k64);
     const __half2 sh1 = __hsub2(*reinterpret_cast<const __half2 *>(&sh1p), k64);
     // the lane's activation row: its own fragment column (MODE 0) or row 0 (MODE 1), chunk t, and
@@ -225,12 +224,12 @@ struct FragQ4K {
       }
     }
 
-    const float d0 = half_bits_to_float(h0.x & 0xffffu) * 16777216.f, d1 = half_bits_to_float(h1.x & 0xffffu) * 16777216.f;
-    const float n0 = half_bits_to_float(h0.x >> 16), n1 = half_bits_to_float(h1.x >> 16);
+    const float d0 = half_bits_to_float(dd0 & 0xffffu) * 16777216.f, d1 = half_bits_to_float(dd1 & 0xffffu) * 16777216.f;
+    const float n0 = half_bits_to_float(dd0 >> 16), n1 = half_bits_to_float(dd1 >> 16);
     if (MODE == 0) {
       // minimum term: one MMA whose k index runs over sub-blocks (hi parts in k 0..7, lo in 8..15);
       // this lane's slots are sub-blocks 2t and 2t + 1, exactly the minima it holds
-      const uint32_t ma = ((v0 >> 12) & 0x3fu) | ((v0 >> 2) & 0x3f0000u), mb = ((v1 >> 12) & 0x3fu) | ((v1 >> 2) & 0x3f0000u);
+      const uint32_t ma = v0 & 0x00ff00ffu, mb = v1 & 0x00ff00ffu;
       const uint2 xs = lds64(xsum + (uint32_t)lane * 8u);
       float cm[4];
       mma16816_first(cm, ma, mb, ma, mb, xs.x, xs.y);
@@ -242,8 +241,8 @@ struct FragQ4K {
     } else {
       // the lane's share of the rows' minimum terms: its two sub-blocks
       const float2 xs = lds64f(xsum + 256u + (uint32_t)t * 8u);
-      const float mt0 = (float)((v0 >> 12) & 63u) * xs.x + (float)((v0 >> 18) & 63u) * xs.y;
-      const float mt1 = (float)((v1 >> 12) & 63u) * xs.x + (float)((v1 >> 18) & 63u) * xs.y;
+      const float mt0 = (float)(v0 & 255u) * xs.x + (float)((v0 >> 16) & 255u) * xs.y;
+      const float mt1 = (float)(v1 & 255u) * xs.x + (float)((v1 >> 16) & 255u) * xs.y;
       acc[0] += d0 * (c[0] + c[1]) - n0 * mt0;
       acc[2] += d1 * (c[2] + c[3]) - n1 * mt1;
     }

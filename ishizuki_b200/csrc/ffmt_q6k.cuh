@@ -121,7 +121,7 @@ struct FragQ6K {
   static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int tasks = uc * 8;
-    constexpr int kBatch = 4;
+    constexpr int kBatch = 8;
     const __half *xl = a.x + (long long)ub0 * 256 + lane * 8;
     if (warp >= tasks) after_loads();  // a warp without a task
     for (int i0 = warp; i0 < tasks; i0 += nw * kBatch) {
