@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <array>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -83,6 +84,9 @@ struct ishi_ctx {
   std::vector<cudaEvent_t> ev_in, ev_done;
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   std::mutex lock;
+  // launch plans already measured on this device, by (format's kernels, output rows, input width):
+  // {K split, warps per panel, panels in parallel, ring}
+  std::map<std::tuple<const void *, long long, long long>, std::array<int, 4>> tuned;
   char last_error[256] = {0};
 };
 
@@ -901,9 +905,19 @@ ishi_status ishi_verify_matmul(ishi_ctx *ctx, const void *x, int rows, const voi
 // the planner's best candidates run a few times on the projection's own tiles (activations of
 // zeros, eight rows) and the fastest stays. The estimate alone is within ~15 % of the best plan.
 static void tune_frag_plan(ishi_ctx *ctx, ishi_projection *p, std::vector<FragPlan> *candidates) {
-  constexpr size_t kTuned = 8;
+  constexpr size_t kTuned = 24;
   constexpr int kLaunches = 4;
   if (candidates->size() < 2) return;
+  // a shape measured before on this context keeps its plan (all layers of a model then agree)
+  const auto key = std::make_tuple((const void *)p->frag.ops, (long long)p->d.n, (long long)p->d.k);
+  const auto known = ctx->tuned.find(key);
+  if (known != ctx->tuned.end()) {
+    for (const FragPlan &c : *candidates)
+      if (c.S == known->second[0] && c.Wu == known->second[1] && c.PP == known->second[2] && c.ring == known->second[3]) {
+        p->frag = c;
+        return;
+      }
+  }
   std::sort(candidates->begin(), candidates->end(), [](const FragPlan &a, const FragPlan &b) { return a.cost < b.cost; });
   if (candidates->size() > kTuned) candidates->resize(kTuned);
   __half *x = nullptr, *y = nullptr;
@@ -926,6 +940,7 @@ static void tune_frag_plan(ishi_ctx *ctx, ishi_projection *p, std::vector<FragPl
   }
   if (ok && best) {
     p->frag = *best;
+    ctx->tuned[key] = {best->S, best->Wu, best->PP, best->ring};
     if (getenv("ISHI_DEBUG_PLAN"))
       fprintf(stderr, "ishi plan n=%lld k=%lld measured: split %d, warps %d x %d, ring %d: %.2f us\n", (long long)p->d.n,
               (long long)p->d.k, best->S, best->Wu, best->PP, best->ring, best_ms * 1e3f / kLaunches);

@@ -49,7 +49,7 @@ constexpr int kFragMaxWarps = ISHI_FRAG_MAX_WARPS;
 constexpr int kFragFewWarps = 20;
 constexpr int kFragMaxRing = 4;   // most tiles per warp-private ring (FragArgs::ring of them are used:
                                   // one is decoded while the others are in flight)
-constexpr int kFragMaxPanels = 8; // most panels a CTA works on in parallel
+constexpr int kFragMaxPanels = 24; // most panels a CTA works on in parallel (one warp each, then)
 constexpr int kFragGroup = 4;     // most units per warp the planner considers
 constexpr int kFragRed = 2;       // partial-tile slots per panel lane: a warp may run this many panels ahead of the slowest
 constexpr int kFragMaxGen = 4;    // most panels of a lane per generation of inbox slots
@@ -179,12 +179,14 @@ __host__ __device__ inline int frag_ring_stride(int tile_bytes) { return (tile_b
 // shared memory of one CTA, in order: activations, the lanes' partial-tile slots, the inbox for the
 // partial panels of the cluster's CTAs, a control block (inbox mbarriers, arrival counters,
 // progress words, abort word), the warps' rings
-// control block: inbox mbarriers [PP][2G] @0, arrival counters [PP][kFragRed] @768, done [PP] @832,
-// abort @864, phases used of every inbox mbarrier [PP][2G] @512, ring mbarriers [warp][kFragMaxRing] @1024
-constexpr uint32_t kFragCtrlBytes = 2048;
+// control block (PP <= 24, G <= 2): inbox mbarriers [PP][2G] @0, phases used of each [PP][2G] @768,
+// arrival counters [PP][kFragRed] @1152, done [PP] @1344, abort @1440, ring mbarriers
+// [warp][kFragMaxRing] @1472
+constexpr uint32_t kFragCtrlBytes = 2304;
 // xregion: the format's activation staging, umax * Fmt::kXBytes + Fmt::kExtraBytes
+// (a panel lane of one warp parks nothing and has no slots)
 __host__ __device__ inline size_t frag_smem_bytes(size_t xregion, int W, int PP, int G, int S, int tile_bytes, int ring) {
-  return xregion + (size_t)W * kFragRed * 512 + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
+  return xregion + (W > PP ? (size_t)W * kFragRed * 512 : 0) + (S > 1 ? (size_t)PP * 2 * G * S * 512 : 0) + kFragCtrlBytes +
          (size_t)W * ring * frag_ring_stride(tile_bytes);
 }
 
@@ -306,16 +308,16 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
 
   const uint32_t xfrag = smem_u32(smem);                                   // [umax][Fmt::kXBytes], then Fmt::kExtraBytes
   const uint32_t red = xfrag + (uint32_t)a.umax * Fmt::kXBytes + Fmt::kExtraBytes;  // [PP][kFragRed][Wu][128 floats]
-  const uint32_t inbox = red + (uint32_t)(W * kFragRed) * 512u;            // [PP][2G][S][128 floats]
+  const uint32_t inbox = red + (Wu > 1 ? (uint32_t)(W * kFragRed) * 512u : 0u);  // [PP][2G][S][128 floats]
   const uint32_t ctrl = inbox + (S > 1 ? (uint32_t)(PP * 2 * G * S) * 512u : 0u);
   const int R = a.ring;  // tiles in this warp's ring
   const uint32_t ring = ctrl + kFragCtrlBytes + (uint32_t)(warp * R) * kStride;
   uint8_t *ctrl_p = smem + (ctrl - xfrag);
   uint64_t *bars = reinterpret_cast<uint64_t *>(ctrl_p);                   // [PP][2G]
-  int *cnt = reinterpret_cast<int *>(ctrl_p + 768);                        // [PP][kFragRed] arrivals of the lane's warps
-  volatile int *done = reinterpret_cast<volatile int *>(ctrl_p + 832);     // [PP] panels of the lane whose partials were added
-  volatile int *abort_word = reinterpret_cast<volatile int *>(ctrl_p + 864);
-  volatile int *uses = reinterpret_cast<volatile int *>(ctrl_p + 512);     // [PP][2G] completed phases of each inbox mbarrier
+  int *cnt = reinterpret_cast<int *>(ctrl_p + 1152);                       // [PP][kFragRed] arrivals of the lane's warps
+  volatile int *done = reinterpret_cast<volatile int *>(ctrl_p + 1344);    // [PP] panels of the lane whose partials were added
+  volatile int *abort_word = reinterpret_cast<volatile int *>(ctrl_p + 1440);
+  volatile int *uses = reinterpret_cast<volatile int *>(ctrl_p + 768);     // [PP][2G] completed phases of each inbox mbarrier
 
   // (divisions by multiplication: the host checks the ranges)
   const int cid = frag_div(blockIdx.x, a.inv_s);
@@ -339,7 +341,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
       mbar_init(bars + i, 1);
       uses[i] = 0;
     }
-    if ((int)threadIdx.x < PP * kFragRed) cnt[threadIdx.x] = 0;
+    for (int i = threadIdx.x; i < PP * kFragRed; i += 32) cnt[i] = 0;
     if ((int)threadIdx.x < PP) done[threadIdx.x] = 0;
     if (threadIdx.x == 0) *abort_word = 0;
     mbar_fence_init();
@@ -351,7 +353,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
   // This warp's tile sequence: its panels in order, in each its units wu + qi * Wu. The fetch
   // cursor runs R - 1 tiles ahead of the compute cursor. Lane 0 issues the copies; every
   // lane keeps the cursor.
-  const uint32_t wbar = ctrl + 1024u + (uint32_t)warp * kFragMaxRing * 8u;  // this warp's ring mbarriers
+  const uint32_t wbar = ctrl + 1472u + (uint32_t)warp * kFragMaxRing * 8u;  // this warp's ring mbarriers
   if (lane == 0) {
 #pragma unroll
     for (int i = 0; i < kFragMaxRing; ++i) mbar_init_u32(wbar + 8u * i, 1);
