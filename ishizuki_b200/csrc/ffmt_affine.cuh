@@ -76,6 +76,9 @@ struct FragAffine {
     return *reinterpret_cast<const uint32_t *>(&r);
   }
 
+  // nothing to set up ahead of the dependency wait
+  static __device__ __forceinline__ void before_wait(const FragArgs &, uint32_t) {}
+
   // Activations of the CTA's column range into fragment order. A warp task is (unit, activation
   // row): lane l loads the eight values k = 8l .. 8l + 7. The fragment of k-step st = kMasks * q + m
   // sits at st * 256 + ((g ^ (q & 3)) * 4 + t) * 8: the xor spreads a store's quads over the banks,

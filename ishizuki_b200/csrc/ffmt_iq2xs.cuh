@@ -83,7 +83,26 @@ struct FragIQ2XS {
 
   static __device__ __forceinline__ uint32_t row_stride(const FragArgs &a) { return (uint32_t)a.umax * 512u + 16u; }
 
-  // Activations of the CTA's column range as they lie in x (rows past M as zeros), and the grid.
+  // What does not depend on the launches before this one, set up ahead of the dependency wait:
+  // the grid. Entry i = eight fp16 magnitudes (the codes are 2 bits each: 0, 1, 2 -> 8, 25, 43);
+  // eight consecutive threads store the eight copies of an entry, 128 contiguous bytes.
+  static __device__ __forceinline__ void before_wait(const FragArgs &a, uint32_t xfrag) {
+    const uint32_t grid = xfrag + (uint32_t)a.umax * kXBytes + kGrid;
+    for (int i = threadIdx.x; i < 512 * 8; i += blockDim.x) {
+      const uint32_t codes = g_iq2xs_frag_codes[i >> 3];
+      uint32_t w[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t c0 = (codes >> (4 * r)) & 3u, c1 = (codes >> (4 * r + 2)) & 3u;
+        const uint32_t h0 = c0 == 0 ? 0x4800u : c0 == 1 ? 0x4e40u : 0x5160u;  // fp16 bits of 8, 25, 43
+        const uint32_t h1 = c1 == 0 ? 0x4800u : c1 == 1 ? 0x4e40u : 0x5160u;
+        w[r] = h0 | (h1 << 16);
+      }
+      sts128u(grid + (uint32_t)i * 16u, make_uint4(w[0], w[1], w[2], w[3]));
+    }
+  }
+
+  // Activations of the CTA's column range as they lie in x (rows past M as zeros).
   // A warp task is (unit, activation row): lane l loads and stores k = 8l .. 8l + 7.
   // after_loads() runs once, when the first batch of loads is in flight. IQ2_XS has no rotation.
   template <class F>
@@ -110,21 +129,6 @@ struct FragIQ2XS {
         if (i >= tasks) break;
         sts128u(xfrag + (uint32_t)(i & 7) * R + (uint32_t)(i >> 3) * 512u + (uint32_t)lane * 16u, v[e]);
       }
-    }
-    // the grid: entry i = eight fp16 magnitudes; the codes are 2 bits each: 0, 1, 2 -> 8, 25, 43
-    const uint32_t grid = xfrag + (uint32_t)a.umax * kXBytes + kGrid;
-    for (int i = threadIdx.x; i < 512; i += blockDim.x) {
-      const uint32_t codes = g_iq2xs_frag_codes[i];
-      uint32_t w[4];
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const uint32_t c0 = (codes >> (4 * r)) & 3u, c1 = (codes >> (4 * r + 2)) & 3u;
-        const uint32_t h0 = c0 == 0 ? 0x4800u : c0 == 1 ? 0x4e40u : 0x5160u;  // fp16 bits of 8, 25, 43
-        const uint32_t h1 = c1 == 0 ? 0x4800u : c1 == 1 ? 0x4e40u : 0x5160u;
-        w[r] = h0 | (h1 << 16);
-      }
-#pragma unroll
-      for (int c = 0; c < 8; ++c) sts128u(grid + (uint32_t)i * 128u + (uint32_t)c * 16u, make_uint4(w[0], w[1], w[2], w[3]));
     }
   }
 

@@ -103,6 +103,9 @@ struct FragQ4K {
   // in flight. Q4_K has no input rotation.
   static __device__ __forceinline__ uint32_t row_stride(const FragArgs &a) { return (uint32_t)a.umax * 512u + 64u; }
 
+  // nothing to set up ahead of the dependency wait
+  static __device__ __forceinline__ void before_wait(const FragArgs &, uint32_t) {}
+
   template <class F>
   static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;

@@ -111,6 +111,9 @@ struct FragQ6K {
     return (uint16_t)(tile_byte(s, p, u, 2 * hw) | ((uint32_t)tile_byte(s, p, u, 2 * hw + 1) << 8));
   }
 
+  // nothing to set up ahead of the dependency wait
+  static __device__ __forceinline__ void before_wait(const FragArgs &, uint32_t) {}
+
   // Activations of the CTA's column range into fragment order. A warp task is (unit, activation
   // row r): lane l loads k = 8l .. 8l + 7, half of group l / 2, i.e. what lanes t = 2(l & 1) and
   // t + 1 of quad r multiply in k-step l / 2. The pair of k-steps i = l / 4 lies at

@@ -386,6 +386,8 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
   // The weight tiles are written by no earlier kernel: their first copies go out at once.
   for (int i = 0; i < R - 1; ++i) fetch();
 
+  Fmt::before_wait(a, xfrag);  // tables that do not depend on earlier launches
+
   // Warm L2 and the address translation with this CTA's slice of x. Only a hint: x may still be
   // written by the kernel before this one, its values are read after the wait below, through L2.
   for (int r = warp; r < a.M; r += (int)(blockDim.x >> 5)) {
