@@ -106,6 +106,31 @@ def test_projection_shapes(type_id, n, k, m):
     assert torch.equal(yt.t().contiguous(), y)
 
 
+@pytest.mark.parametrize("type_id", STREAMED)
+def test_properties_at_full_size(type_id):
+    """Size-independent properties on the benchmark's gate shape: doubling the activations doubles
+    every output exactly (powers of two pass through fp16 and fp32 unchanged), a zero row gives
+    zeros, the rows of x do not influence each other, and the product is additive in x within
+    the fp16 tolerance."""
+    n, k = 17408, 5120
+    rng = np.random.default_rng(int(type_id))
+    lin = PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k)))
+    x = dev(synth.activations(rng, 8, k))
+    y = lin(x)
+    assert torch.equal(lin(x * 2), y * 2)
+    x0 = x.clone()
+    x0[3] = 0
+    y0 = lin(x0)
+    assert not y0[3].any()
+    assert torch.equal(y0[[0, 1, 2, 4, 5, 6, 7]], y[[0, 1, 2, 4, 5, 6, 7]])
+    assert torch.equal(lin(x[[7, 6, 5, 4, 3, 2, 1, 0]]), y[[7, 6, 5, 4, 3, 2, 1, 0]])
+    x2 = dev(synth.activations(rng, 8, k))
+    both = lin(x + x2).float()
+    parts = y.float() + lin(x2).float()
+    assert float((both - parts).abs().max() / parts.abs().max()) < 2 * TOL
+    lin.ctx.poll()
+
+
 def test_product_guards():
     blocks = torch.zeros(4 * 74, dtype=torch.uint8, device="cuda")
     wide = torch.zeros((17, 256), dtype=torch.float16, device="cuda")
