@@ -16,16 +16,17 @@
 // weight, different order.
 //
 // Work. K is cut into S column ranges and the kernel is launched as thread-block clusters of S
-// CTAs: CTA r of a cluster stages the activations of column range r into shared memory once, in
-// fragment order, and all CTAs of a cluster walk the same run of 16-row panels, dealt to the
-// clusters in equal contiguous runs. A CTA works on PP panels at a time ("panel lanes"), Wu warps
+// CTAs (S = 1: no cluster): CTA r of a cluster stages the activations of column range r into shared
+// memory once, laid out as its format's decoder reads them, and all CTAs of a cluster walk the same
+// run of 16-row panels, dealt to the clusters in equal contiguous runs. A CTA works on PP panels at a time ("panel lanes"), Wu warps
 // per lane: warp (lane wp, position wu) takes panels wp, wp + PP, ... of the cluster's run and in
 // each the units wu, wu + Wu, ... of the CTA's column range, streaming its tiles through a private
 // ring in shared memory: one bulk async copy per tile (the copy engine, not the load/store unit,
 // moves the bytes), completion counted on the ring slot's own mbarrier. No producer warp, no
 // cross-warp wait on the data path.
 //
-// Reduction, without a CTA-wide barrier. A warp that has finished a panel parks its 16 x 8 partial
+// Reduction, without a CTA-wide barrier. With Wu = 1 a warp owns its panels whole and there is
+// nothing to add up inside the CTA. Else a warp that has finished a panel parks its 16 x 8 partial
 // tile in the lane's slot ring and bumps the slot's arrival counter; the warp that arrives last
 // adds the lane's partials in warp order. With S > 1 it sends the CTA's partial panel into the
 // shared memory of the panel's leader CTA (distributed shared memory, st.async counted on an
@@ -45,6 +46,7 @@ constexpr int kFragRows = 16;
 #endif
 // The kernel is compiled for two block sizes: up to kFragFewWarps warps with 96 registers per
 // thread (the decoders' loads then run further ahead of their use), and up to kFragMaxWarps with 80.
+// (A third one, 16 warps with 128 registers, measured no faster.)
 constexpr int kFragMaxWarps = ISHI_FRAG_MAX_WARPS;
 constexpr int kFragFewWarps = 20;
 constexpr int kFragMaxRing = 4;   // most tiles per warp-private ring (FragArgs::ring of them are used:
