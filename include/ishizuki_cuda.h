@@ -175,8 +175,9 @@ ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_h
 
 /* A list of projections in one call, each with its own host input x_hosts[i] [rows, k_i] and host
  * output y_hosts[i] [rows, n_i] (page-locked buffers for the copies to overlap): the x copies, the
- * products and the y copies are pipelined over three streams, and the caller's stream ends behind
- * all of them, so one cudaStreamSynchronize(stream) completes the whole list. The projections
+ * products and the y copies are pipelined over three streams in chunks of sixteen entries, and the
+ * caller's stream ends behind all of them, so one cudaStreamSynchronize(stream) completes the whole
+ * list. The projections
  * must share a context and are independent of each other (none reads another's output). */
 ishi_status ishi_projection_apply_host_batch(ishi_projection *const *projections,
                                              const void *const *x_hosts, int rows,

@@ -1203,20 +1203,31 @@ ishi_status ishi_projection_apply_host_batch(ishi_projection *const *ps, const v
   }
   // Three lanes: x copies run ahead on one stream, the products follow on the caller's stream as
   // their inputs land, the y copies trail on a third; the caller's stream ends behind all of them.
+  // The lanes hand over in chunks of kChunk entries, not entry by entry: an event between two
+  // product kernels would serialise them, inside a chunk they follow each other with programmatic
+  // dependent launch as in a plain sequence of applies.
+  constexpr int kChunk = 16;
   ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_begin, st));
   ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->ev_begin, 0));
   ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_begin, 0));
-  for (int i = 0; i < count; ++i) {
-    ishi_projection *p = ps[i];
-    const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * p->d.n * sizeof(__half);
-    ISHI_CUDA(ctx, cudaMemcpyAsync(p->host_x, x_hosts[i], xb, cudaMemcpyHostToDevice, ctx->copy_in));
-    ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_in[i], ctx->copy_in));
-    ISHI_CUDA(ctx, cudaStreamWaitEvent(st, ctx->ev_in[i], 0));
-    ishi_status s = ishi_projection_apply(p, p->host_x, rows, p->host_y, p->d.n, 0, stream);
-    if (s != ISHI_OK) return s;
-    ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_done[i], st));
-    ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[i], 0));
-    ISHI_CUDA(ctx, cudaMemcpyAsync(y_hosts[i], p->host_y, yb, cudaMemcpyDeviceToHost, ctx->copy_out));
+  for (int c0 = 0; c0 < count; c0 += kChunk) {
+    const int c1 = std::min(count, c0 + kChunk);
+    for (int i = c0; i < c1; ++i) {
+      const size_t xb = (size_t)rows * ps[i]->d.k * sizeof(__half);
+      ISHI_CUDA(ctx, cudaMemcpyAsync(ps[i]->host_x, x_hosts[i], xb, cudaMemcpyHostToDevice, ctx->copy_in));
+    }
+    ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_in[c0], ctx->copy_in));
+    ISHI_CUDA(ctx, cudaStreamWaitEvent(st, ctx->ev_in[c0], 0));
+    for (int i = c0; i < c1; ++i) {
+      ishi_status s = ishi_projection_apply(ps[i], ps[i]->host_x, rows, ps[i]->host_y, ps[i]->d.n, 0, stream);
+      if (s != ISHI_OK) return s;
+    }
+    ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_done[c0], st));
+    ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[c0], 0));
+    for (int i = c0; i < c1; ++i) {
+      const size_t yb = (size_t)rows * ps[i]->d.n * sizeof(__half);
+      ISHI_CUDA(ctx, cudaMemcpyAsync(y_hosts[i], ps[i]->host_y, yb, cudaMemcpyDeviceToHost, ctx->copy_out));
+    }
   }
   ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_end, ctx->copy_out));
   ISHI_CUDA(ctx, cudaStreamWaitEvent(st, ctx->ev_end, 0));
