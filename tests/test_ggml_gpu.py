@@ -163,19 +163,27 @@ def test_host_buffer_entry_points_agree():
         assert np.array_equal(y2.view(np.uint16), w.numpy().view(np.uint16))
 
 
-@pytest.mark.parametrize("plan", ["1,2,1", "1,3,2", "2,1,2", "2,2,4", "3,1,2", "4,2,2", "5,1,4", "8,1,4"])
-def test_every_launch_plan_gives_the_same_product(plan, monkeypatch):
+@pytest.mark.parametrize("type_id", STREAMED)
+@pytest.mark.parametrize("plan", ["1,2,1", "1,3,2", "2,1,2", "2,2,4", "3,1,2", "4,2,2", "5,1,4", "8,1,4",
+                                  "2,11,12", "1,21,16", "2,4,6,2", "3,7,8", "2,6,5"])
+def test_every_launch_plan_gives_the_same_product(plan, type_id, monkeypatch):
     """The warp-level kernel under forced launch plans (K split = cluster size, units per warp,
-    panels in parallel), on a shape with a ragged last panel and an uneven K split."""
+    panels in parallel, optionally the ring depth), on a shape with a ragged last panel and an
+    uneven K split: plans with and without clusters, with several warps per panel and with a warp
+    owning whole panels."""
     monkeypatch.setenv("ISHI_FRAG_PLAN", plan)
     rng = np.random.default_rng(21)
     n, k = 1000, 5120 + 256
-    blocks = synth.q4k_blocks(rng, n, k)
-    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks), GGMLType.q4K, (n, k)))
+    blocks = synth.ggml_blocks(rng, int(type_id), n, k)
+    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks), type_id, (n, k)))
+    want_plan = [int(v) for v in plan.split(",")]
+    if lin.plan[0] == 0:
+        pytest.skip("this plan does not fit shared memory for this format (the tcgen05 kernel took the weight)")
+    assert lin.plan[0] == want_plan[0] and lin.plan[2] == want_plan[2], "the forced plan was not taken"
     for m in (1, 8, 11):
         x = synth.activations(rng, m, k)
         got = lin(dev(x)).cpu().numpy()
-        want32, _ = oracle.ggml_matmul(int(GGMLType.q4K), blocks, x, n)
+        want32, _ = oracle.ggml_matmul(int(type_id), blocks, x, n)
         err = float(np.abs(got.astype(np.float64) - want32.astype(np.float64)).max() / np.abs(want32).max())
         assert err < 2e-3, (plan, m, err)
     lin.ctx.poll()
