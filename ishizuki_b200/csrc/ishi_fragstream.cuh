@@ -369,10 +369,7 @@ __global__ void __launch_bounds__(MAXW * 32, 1) frag_kernel(const FragArgs a) {
   const long long step_unit = (long long)Wu * kTile;
   const long long step_panel = ((long long)PP * a.units - (long long)per * Wu) * kTile;
   auto fetch = [&]() {
-    if (f_left > 0 && lane == 0) {
-      mbar_arrive_expect_tx_u32(wbar + 8u * f_idx, (uint32_t)kTile);
-      bulk_g2s_u32(f_slot, f_src, (uint32_t)kTile, wbar + 8u * f_idx);
-    }
+    bulk_g2s_if(f_left > 0 && lane == 0, f_slot, f_src, (uint32_t)kTile, wbar + 8u * f_idx);
     --f_left;
     f_src += step_unit;
     if (++f_qi == per) {

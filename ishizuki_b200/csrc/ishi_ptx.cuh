@@ -83,6 +83,17 @@ __device__ __forceinline__ void bulk_g2s_u32(uint32_t dst, const void *src_gmem,
                "l"(src_gmem), "r"(bytes), "r"(bar)
                : "memory");
 }
+// arrive.expect_tx + bulk copy onto the same mbarrier, both under one predicate: a lane that does
+// not issue them runs through without a branch
+__device__ __forceinline__ void bulk_g2s_if(bool go, uint32_t dst, const void *src_gmem, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %0, 0;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%4], %3;\n\t"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%1], [%2], %3, [%4];\n\t}"
+      ::"r"((uint32_t)go), "r"(dst), "l"(src_gmem), "r"(bytes), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
