@@ -369,6 +369,15 @@ def format_table(peak: float) -> dict:
         row = {"weight_mb": lins[0].weightBytes / 1e6}
         for m in row_counts:
             row["m%d" % m] = measure(lins, m, k)
+        if fmt in ("q4_k", "q6_k", "iq2_xs") and not only:
+            # the same format on the tcgen05 kernel (ISHI_KERNEL=tcgen05 at projection create)
+            os.environ["ISHI_KERNEL"] = "tcgen05"
+            try:
+                slow = [make(fmt, n, k) for _ in range(copies)]
+            finally:
+                del os.environ["ISHI_KERNEL"]
+            row["m8_tcgen05_kernel"] = measure(slow, 8, k)
+            del slow
         if fmt in ("q4_k", "affine4_g64") and not only:
             # the single-row CUDA-core variant beside the tensor-core kernel (ISHI_ROUTE_GEMV)
             BonsaiRuntime.route = _lib.ROUTE_GEMV

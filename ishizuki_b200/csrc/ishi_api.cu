@@ -385,6 +385,9 @@ ishi_status run_rows(ishi_ctx *ctx, const RowPlan &pl, const Workspace &ws, int 
 // The fragment decoder that serves a weight, or null (the tcgen05 kernel then takes it, as it does
 // when no plan of the warp-level kernel fits shared memory: very wide inputs).
 const FragOps *frag_ops_for(const ishi_weight_desc &d) {
+  // ISHI_KERNEL=tcgen05: every weight goes to the tcgen05 kernel (to compare the two kernels on one format)
+  const char *which = getenv("ISHI_KERNEL");
+  if (which && strcmp(which, "tcgen05") == 0) return nullptr;
   if (d.kind == ISHI_KIND_GGML) {
     if (d.ggml_type == ISHI_GGML_Q4_K) return frag_ops_q4k();
     if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
@@ -926,24 +929,40 @@ static void tune_frag_plan(ishi_ctx *ctx, ishi_projection *p, std::vector<FragPl
             cudaMalloc(&y, (size_t)8 * p->d.n * sizeof(__half)) == cudaSuccess &&
             cudaMemset(x, 0, (size_t)8 * p->d.k * sizeof(__half)) == cudaSuccess && cudaEventCreate(&e0) == cudaSuccess &&
             cudaEventCreate(&e1) == cudaSuccess;
+  // one timing: a warm-up launch, then `launches` back to back between two events
+  auto time_plan = [&](const FragPlan &c, int launches, float *ms_per_launch) {
+    bool fine = run_frag(ctx, c, p->ws, p->d, x, 8, y, p->d.n, 0, false, true, false, 0) == ISHI_OK;
+    if (fine) fine = cudaEventRecord(e0, 0) == cudaSuccess;
+    for (int r = 0; fine && r < launches; ++r) fine = run_frag(ctx, c, p->ws, p->d, x, 8, y, p->d.n, 0, false, true, false, 0) == ISHI_OK;
+    if (fine) fine = cudaEventRecord(e1, 0) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+    float ms = 0.f;
+    if (fine) fine = cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;
+    *ms_per_launch = ms / launches;
+    return fine;
+  };
+  // first pass over all candidates, then the best few again with more launches (the first pass
+  // alone picks among near-equal plans by noise)
+  constexpr size_t kFinalists = 4;
+  std::vector<std::pair<float, const FragPlan *>> timed;
+  for (size_t i = 0; ok && i < candidates->size(); ++i) {
+    float ms = 0.f;
+    ok = time_plan((*candidates)[i], kLaunches, &ms);
+    if (ok) timed.push_back({ms, &(*candidates)[i]});
+  }
+  std::sort(timed.begin(), timed.end(), [](const auto &a, const auto &b) { return a.first < b.first; });
   float best_ms = 0.f;
   const FragPlan *best = nullptr;
-  for (size_t i = 0; ok && i < candidates->size(); ++i) {
-    const FragPlan &c = (*candidates)[i];
-    ok = run_frag(ctx, c, p->ws, p->d, x, 8, y, p->d.n, 0, false, true, false, 0) == ISHI_OK;  // warm-up
-    if (ok) ok = cudaEventRecord(e0, 0) == cudaSuccess;
-    for (int r = 0; ok && r < kLaunches; ++r) ok = run_frag(ctx, c, p->ws, p->d, x, 8, y, p->d.n, 0, false, true, false, 0) == ISHI_OK;
-    if (ok) ok = cudaEventRecord(e1, 0) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+  for (size_t i = 0; ok && i < timed.size() && i < kFinalists; ++i) {
     float ms = 0.f;
-    if (ok) ok = cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;
-    if (ok && (!best || ms < best_ms)) best = &c, best_ms = ms;
+    ok = time_plan(*timed[i].second, 4 * kLaunches, &ms);
+    if (ok && (!best || ms < best_ms)) best = timed[i].second, best_ms = ms;
   }
   if (ok && best) {
     p->frag = *best;
     ctx->tuned[key] = {best->S, best->Wu, best->PP, best->ring};
     if (getenv("ISHI_DEBUG_PLAN"))
       fprintf(stderr, "ishi plan n=%lld k=%lld measured: split %d, warps %d x %d, ring %d: %.2f us\n", (long long)p->d.n,
-              (long long)p->d.k, best->S, best->Wu, best->PP, best->ring, best_ms * 1e3f / kLaunches);
+              (long long)p->d.k, best->S, best->Wu, best->PP, best->ring, best_ms * 1e3f);
   } else {
     cudaGetLastError();  // keep the estimate's choice
   }

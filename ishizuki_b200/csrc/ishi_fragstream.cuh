@@ -2,11 +2,11 @@
 // on mma.sync (m16n8k16, weights on the M side, activation rows on the N side), with a CUDA-core
 // variant for a single row.
 //
-// Why not tcgen05 here: one tcgen05.mma of 128 weight rows x 16 k costs about 100 cycles of the
-// SM's tensor pipe whatever N is (measured for N = 16 ... 128), which caps a few-row product at
-// ~20 weights per clock and SM; eight activation rows fill an m16n8k16 fragment exactly, and the
-// warp-level instruction sustains several times that. The tcgen05 kernel stays for the formats
-// that have no fragment decoder.
+// Why not tcgen05 here: eight activation rows fill an m16n8k16 fragment exactly, twenty-odd warps
+// per SM decode in registers right beside the MMA, and on the same weights this kernel measures
+// about twice as fast as the tcgen05 kernel (ishi_rowstream.cuh: 128 weight rows per instruction,
+// four decode warps per CTA feeding tensor memory). That kernel stays for the formats that have
+// no fragment decoder and for inputs too wide for this one's shared memory.
 //
 // Layout. The weight is re-tiled once, when the projection is created, into fragment order: a
 // tile is 16 output rows x 256 k (one unit), stored as [16-byte piece][lane] so that every
