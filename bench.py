@@ -18,7 +18,8 @@ The metric is weight GB/s: compressed weight bytes streamed per second (GB = 1e9
 reference's own convention (block bytes only). With N > 1 every matrix is sharded along its
 output rows across the ranks (strong scaling: the same pass at every N); by default the product
 kernels store their rows into every rank's copy of the output over NVLink (no collective), with
-ISHI_BENCH_NCCL=1 one NCCL all-gather per launch assembles them instead. After the timed region
+ISHI_BENCH_NCCL=1 one NCCL all-gather per launch assembles them instead (ISHI_BENCH_NO_PEER_WAIT=1,
+a diagnostic: the launches do not wait for the other ranks' previous launch). After the timed region
 every rank checks exchanged outputs against the ranks' shards recomputed locally.
 
 Prints one JSON line (rank 0).
@@ -523,7 +524,7 @@ def run_ours(args) -> dict | None:
             if exchange is not None:
                 # every kernel stores its rows into all ranks' copies; it first waits for the other
                 # ranks' previous launch, whose outputs a layer stack's data flow makes it depend on
-                exchange.apply(lin, x, y_local, row0, wait_previous=True)
+                exchange.apply(lin, x, y_local, row0, wait_previous=os.environ.get("ISHI_BENCH_NO_PEER_WAIT") != "1")
             elif world > 1:
                 nccl_group.apply(lin, x, y_full)  # ishi_projection_apply_sharded: product + ncclAllGather
             else:
