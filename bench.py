@@ -402,10 +402,10 @@ def format_table(peak: float) -> dict:
             BonsaiRuntime.route = _lib.ROUTE_AUTO
         table[name] = row
         del lins
-    # one of the eight other GGML block types (one warp per output row, not tuned): IQ4_XS
+    # one of the eight other GGML block types (warp-level kernel through the dense decoder): IQ4_XS
     lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(GGMLType.iq4Xs), n, k)), GGMLType.iq4Xs, (n, k)))
             for _ in range(2)]
-    table["iq4_xs_row_kernel"] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
+    table["iq4_xs_dense_decoder"] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
     del lins
     torch.cuda.empty_cache()
     # configuration 1: a single 4096 x 4096 affine 4-bit group-64 projection (32 distinct weights)

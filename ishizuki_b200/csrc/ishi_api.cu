@@ -25,6 +25,8 @@ namespace ishi {
 const FragOps *frag_ops_q4k();
 const FragOps *frag_ops_q6k();
 const FragOps *frag_ops_iq2xs();
+const FragOps *frag_ops_ggml_a(int type);
+const FragOps *frag_ops_ggml_b(int type);
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
 const FragOps *frag_ops_affine2(int group_size, bool bf16);
 const RowOps *row_ops_ggml(int type);
@@ -392,7 +394,8 @@ const FragOps *frag_ops_for(const ishi_weight_desc &d) {
     if (d.ggml_type == ISHI_GGML_Q4_K) return frag_ops_q4k();
     if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
     if (d.ggml_type == ISHI_GGML_IQ2_XS) return frag_ops_iq2xs();
-    return nullptr;
+    if (const FragOps *ops = frag_ops_ggml_a(d.ggml_type)) return ops;
+    return frag_ops_ggml_b(d.ggml_type);  // the other block types, through the dense decoder
   }
   if (d.scale_dtype != ISHI_DT_F16 && d.scale_dtype != ISHI_DT_BF16) return nullptr;
   const bool bf16 = d.scale_dtype == ISHI_DT_BF16;

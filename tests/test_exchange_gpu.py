@@ -30,14 +30,17 @@ def _projection(fmt, rng, n, k):
         return PackedLinear(ggml=GGUFBlocks(dev(synth.q4k_blocks(rng, n, k)), GGMLType.q4K, (n, k)))
     if fmt == "q6_k":
         return PackedLinear(ggml=GGUFBlocks(dev(synth.q6k_blocks(rng, n, k)), GGMLType.q6K, (n, k)))
-    if fmt in ("iq2_xs", "iq4_xs"):  # the tcgen05 kernel / the one-warp-per-row kernel: product, then a publishing kernel
+    if fmt in ("iq2_xs", "iq4_xs"):
         type_id = GGMLType.iq2Xs if fmt == "iq2_xs" else GGMLType.iq4Xs
         return PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k)))
+    if fmt == "affine8":  # the tcgen05 kernel: the product, then a publishing kernel
+        w, s, b = synth.affine_pack(rng, n, k, 8, 64, np.float16)
+        return PackedLinear(dev(w), dev(s), dev(b), None, 0, groupSize=64, bits=8)
     w, s, b = synth.affine_pack(rng, n, k, 4, 64, np.float16)
     return PackedLinear(dev(w), dev(s), dev(b), None, 0, groupSize=64, bits=4)
 
 
-@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "affine4", "iq2_xs", "iq4_xs"])
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "affine4", "iq2_xs", "iq4_xs", "affine8"])
 @pytest.mark.parametrize("rows", [1, 5, 8])
 def test_single_rank_exchange_matches_projection(rows, fmt):
     rng = np.random.default_rng(rows)

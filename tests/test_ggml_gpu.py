@@ -258,6 +258,23 @@ def test_stacked_q6k_matrices():
         assert rel_err(piece.cpu().numpy(), want32) < TOL
 
 
+def test_stacked_matrices_of_another_block_type():
+    """The other GGML block types run on the warp-level kernel through the dense decoder and stack
+    like the rest."""
+    rng = np.random.default_rng(14)
+    k, sizes = 1024, (40, 128)
+    parts = [synth.ggml_blocks(rng, int(GGMLType.iq4Xs), n, k) for n in sizes]
+    fused = FusedLinear([GGUFBlocks(dev(b), GGMLType.iq4Xs, (n, k)) for b, n in zip(parts, sizes)])
+    x = synth.activations(rng, 8, k)
+    y = fused(dev(x))
+    torch.cuda.synchronize()
+    fused.ctx.poll()
+    assert all(v > 0 for v in fused.plan)
+    for piece, blocks, n in zip(fused.split(y), parts, sizes):
+        want32, _ = oracle.ggml_matmul(int(GGMLType.iq4Xs), blocks, x, n)
+        assert rel_err(piece.cpu().numpy(), want32) < TOL
+
+
 def test_stacked_affine_packs():
     rng = np.random.default_rng(9)
     k, sizes = 2048, (256, 100)
@@ -293,10 +310,9 @@ def test_stacking_guards():
     b = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 1024)), GGMLType.q4K, (32, 1024))
     with pytest.raises(ValueError):
         FusedLinear([a, b])  # different input widths
-    other = [GGUFBlocks(dev(synth.ggml_blocks(rng, int(GGMLType.iq4Xs), 32, 512)), GGMLType.iq4Xs, (32, 512))
-             for _ in range(2)]
+    packs = [synth.affine_pack(rng, 64, 512, 8, 64, np.float16) for _ in range(2)]
     with pytest.raises(IshizukiError) as err:
-        FusedLinear(other)  # no fragment decoder: cannot be stacked
+        FusedLinear([(dev(w), dev(sc), dev(b)) for w, sc, b in packs], groupSize=64, bits=8)  # 8-bit packs run on the tcgen05 kernel: cannot be stacked
     assert err.value.status == _lib.E_UNSUPPORTED
 
 
