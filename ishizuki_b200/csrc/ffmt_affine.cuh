@@ -87,6 +87,10 @@ struct FragAffine {
   // used (the kernel issues its first weight copies there, behind the activations).
   template <class F>
   static __device__ __forceinline__ void stage_x(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
+    if (BITS == 2 && GS == 128 && a.rot_block == 128 && !a.rot_signs) {
+      stage_x_rot128(a, xfrag, ub0, uc, after_loads);
+      return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int tasks = uc * 8;
     constexpr int kBatch = 8;
@@ -151,6 +155,108 @@ struct FragAffine {
         if ((lane & (GS / 8 - 1)) == 0)
           asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + kSums + (uint32_t)((lane / (GS / 8)) * 8 + g) * 4u), "f"(s)
                        : "memory");
+      }
+    }
+  }
+
+  // +1 or -1 in fp16 by the parity of v
+  static __device__ __forceinline__ uint32_t sign_half(int v) { return 0x3c00u | ((uint32_t)(__popc(v) & 1) << 15); }
+  static __device__ __forceinline__ uint32_t pack_rn(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+
+  // The 2-bit staging with the block Hadamard rotation of 128 (no sign vector) on the tensor
+  // cores. With k = 8 i + j inside a block (i < 16, j < 8) the natural-order transform factors as
+  // H128 = H16 (x) H8, so the rotated block, seen as the matrix Y[j'][i'], is H8 * X^T * H16:
+  //   stage 1: Z[j'][i] = sum_j H8[j'][j] x[8 i + j]. One m16n8k16 takes both blocks of a unit:
+  //     A = [H8 0; 0 H8] (rows j' of the first block, then of the second), B rows k = j of the
+  //     first block then of the second, columns i of one half (eight of the sixteen): lane
+  //     (g, t) supplies the 32-bit word g * 4 + t of that half, a coalesced load.
+  //   stage 2: Y[j'][i'] = sum_i Z[j'][i] H16[i][i'], A = Z of both blocks (the fp32 sums of
+  //     stage 1 as fp16 high and low parts, two MMAs, so nothing is lost to the fp16 operand),
+  //     B = H16, columns i' of one half.
+  // The fp32 result times 1 / sqrt(128) is rounded to fp16 as the butterfly's is; the two agree
+  // to fp32 rounding. Lane (g, t) ends up with the values k' = 16 (4 h + t) + g and + 8 of each
+  // block: the codes g and g + 8 of the block's word 4 h + t, which are one B register of the
+  // product's k-step (quad 2 block + h, mask g % 4), low register when g < 4.
+  template <class F>
+  static __device__ __forceinline__ void stage_x_rot128(const FragArgs &a, uint32_t xfrag, int ub0, int uc, F &&after_loads) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int tasks = uc * 8;
+    constexpr int kBatch = 8;
+    const uint32_t h8 = sign_half(g & (2 * t)) | (sign_half(g & (2 * t + 1)) << 16);
+    uint32_t h16[2][2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int n = 8 * h + g;
+      h16[h][0] = sign_half(n & (2 * t)) | (sign_half(n & (2 * t + 1)) << 16);
+      h16[h][1] = sign_half(n & (2 * t + 8)) | (sign_half(n & (2 * t + 9)) << 16);
+    }
+    const int m = g & 3;
+    const uint32_t down1 = (uint32_t)(15 - 2 * m) << 10;  // 2^-(2 m) in fp16
+    const uint32_t down = down1 | (down1 << 16);
+    const float scale = 1.0f / sqrtf(128.f);
+    const uint32_t *xl = reinterpret_cast<const uint32_t *>(a.x + (long long)ub0 * 256) + lane;
+    const long long row_words = a.K >> 1;
+    if (warp >= tasks) after_loads();
+    for (int i0 = warp; i0 < tasks; i0 += nw * kBatch) {
+      uint32_t v[kBatch][4];  // [block * 2 + half]
+#pragma unroll
+      for (int e = 0; e < kBatch; ++e) {
+        const int i = i0 + e * nw;
+        const bool live = i < tasks && (i & 7) < a.M;
+        const uint32_t *src = xl + (long long)(i & 7) * row_words + (i >> 3) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[e][c] = live ? __ldg(src + 32 * c) : 0u;
+      }
+      if (i0 == warp) after_loads();
+#pragma unroll
+      for (int e = 0; e < kBatch; ++e) {
+        const int i = i0 + e * nw;
+        if (i >= tasks) break;
+        const int r = i & 7;
+        const uint32_t base = xfrag + (uint32_t)(i >> 3) * kXBytes;
+        uint32_t zh[4], zl[4];  // stage 2's A registers: (block 0, half 0), (block 1, half 0), (block 0, half 1), (block 1, half 1)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float z[4];
+          mma16816_first(z, h8, 0u, 0u, h8, v[e][h], v[e][2 + h]);
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            const uint32_t hi = pack_rn(z[2 * b], z[2 * b + 1]);
+            const float2 hf = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+            zh[2 * h + b] = hi;
+            zl[2 * h + b] = pack_rn(z[2 * b] - hf.x, z[2 * b + 1] - hf.y);
+          }
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float y[4];
+          mma16816_first(y, zh[0], zh[1], zh[2], zh[3], h16[h][0], h16[h][1]);
+          mma16816(y, zl[0], zl[1], zl[2], zl[3], h16[h][0], h16[h][1]);
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            const uint32_t pr = pack_rn(__fmul_rn(y[2 * b], scale), __fmul_rn(y[2 * b + 1], scale));
+            const float2 pf = __half22float2(*reinterpret_cast<const __half2 *>(&pr));
+            sum[b] += pf.x + pf.y;
+            const __half2 sc = __hmul2(*reinterpret_cast<const __half2 *>(&pr), *reinterpret_cast<const __half2 *>(&down));
+            const int q = 2 * b + h;
+            sts32(base + (uint32_t)(4 * q + m) * 256u + (uint32_t)(((r ^ q) * 4 + t) * 8 + (g >> 2) * 4),
+                  *reinterpret_cast<const uint32_t *>(&sc));
+          }
+        }
+        // fp32 sums of the rounded values over each block (the group of the bias term): the lower
+        // half warp collects the first block, the upper half the second
+        const bool up = lane & 16;
+        float keep = up ? sum[1] : sum[0];
+        keep += __shfl_xor_sync(0xffffffffu, up ? sum[0] : sum[1], 16);
+#pragma unroll
+        for (int d = 8; d; d >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, d);
+        if ((lane & 15) == 0)
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(base + kSums + (uint32_t)((lane >> 4) * 8 + r) * 4u), "f"(keep) : "memory");
       }
     }
   }

@@ -134,6 +134,9 @@ __device__ __forceinline__ void cp_async_wait() {
 __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t a) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
+}
 // (not volatile: callers tie the address to the barrier that publishes the data)
 __device__ __forceinline__ float lds32f(uint32_t addr) {
   float v;

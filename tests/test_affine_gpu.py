@@ -108,10 +108,13 @@ def test_ternary_rotated_projection(n, k):
         xr = oracle.hadamard_rotate(x, 128)
         want32, _ = oracle.affine_matmul(w, sbits, bbits, 2, 128, xr, bf16=True)
         assert rel_err(y.cpu().numpy(), want32) < TOL
-        # rotate + applyRotated is the same product in two calls
+        # rotate + applyRotated is the same product in two calls. The product kernel rotates this
+        # case on the tensor cores, the rotation kernel by butterflies: the two agree to fp32
+        # rounding, the outputs to a unit in the last place of fp16
         xr_dev = lin.rotate(dev(x))
         assert np.array_equal(xr_dev.cpu().numpy().view(np.uint16), xr.view(np.uint16))
-        assert torch.equal(lin.applyRotated(xr_dev), y)
+        two = lin.applyRotated(xr_dev).cpu().numpy().astype(np.float32)
+        assert rel_err(two, y.cpu().numpy().astype(np.float32)) < 5e-4
     lin.ctx.poll()
 
 
