@@ -440,6 +440,40 @@ def format_table(peak: float) -> dict:
     table["ternary2_g128_h128_layer"] = row
     del layers
     torch.cuda.empty_cache()
+    # An MLP block (Q4_K, M = 8): down(silu(gate(x)) * up(x)). "gated": gate and up as one launch
+    # whose epilogue writes silu(gate) * up, then down: two launches. "stacked_and_elementwise":
+    # the stacked gate+up launch, silu(gate) * up as element-wise kernels of the host framework
+    # (what the reference does through MLX), then down.
+    blocks = 4
+    mlps = []
+    for _ in range(blocks):
+        parts = [GGUFBlocks(dev(synth.q4k_blocks(rng, 17408, 5120)), GGMLType.q4K, (17408, 5120)) for _ in range(2)]
+        mlps.append((FusedLinear(parts, gated=True), FusedLinear(parts), make("q4_k", 5120, 17408)))
+        del parts
+    x = dev(synth.activations(rng, 8, 5120))
+    h = torch.empty((8, 17408), dtype=torch.float16, device="cuda")
+    gu = torch.empty((8, 2 * 17408), dtype=torch.float16, device="cuda")
+    ys = [torch.empty((8, 5120), dtype=torch.float16, device="cuda") for _ in range(blocks)]
+
+    def run_gated():
+        for (gated, _, down), y in zip(mlps, ys):
+            gated(x, out=h)
+            down(h, out=y)
+
+    def run_stacked():
+        for (_, stacked, down), y in zip(mlps, ys):
+            stacked(x, out=gu)
+            torch.mul(torch.nn.functional.silu(gu[:, :17408]), gu[:, 17408:], out=h)
+            down(h, out=y)
+
+    mb = sum(lin.weightBytes for lin in mlps[0][1:]) / 1e6
+    row = {"weight_mb": mb}
+    for name, run in (("gated", run_gated), ("stacked_and_elementwise", run_stacked)):
+        us = timed_graph(run) / blocks
+        row[name] = {"us_per_block": round(us, 2), "gbs": round(mb * 1e3 / us, 1), "frac_of_peak": round(mb * 1e3 / us / peak, 3)}
+    table["q4_k_mlp_block_m8"] = row
+    del mlps
+    torch.cuda.empty_cache()
     return table
 
 

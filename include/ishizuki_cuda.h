@@ -124,6 +124,18 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc,
  * (ISHI_E_UNSUPPORTED otherwise). */
 ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
                                          ishi_projection **out);
+/* The MLP's gate and up projections as ONE projection whose output is the input of downProj:
+ * y = silu(x . gate^T) * (x . up^T), [rows, n] with n the height of either weight
+ * (Sources/IshizukiKit/Text/Attention.swift:251, where the reference runs two projections and two
+ * element-wise kernels). The rows of the two weights are interleaved by eights in the tiled copy,
+ * so one accumulator fragment of the kernel holds a gate row and its up row and the epilogue
+ * combines them: no [rows, 2 n] intermediate is written. Roundings as on the reference's fp16
+ * arrays: both products, the sigmoid, gate * sigmoid and the final product are each rounded to
+ * fp16, the arithmetic is fp32. Same formats as ishi_projection_create_fused; both descriptors
+ * must agree as there, n the same for both and a multiple of 8 (ISHI_E_SHAPE otherwise).
+ * ishi_projection_output_dim returns n, ishi_projection_weight_bytes the bytes of both weights. */
+ishi_status ishi_projection_create_gated(ishi_ctx *ctx, const ishi_weight_desc *gate,
+                                         const ishi_weight_desc *up, ishi_projection **out);
 void ishi_projection_destroy(ishi_projection *p);
 int64_t ishi_projection_input_dim(const ishi_projection *p);  /* Projection.inputDim */
 int64_t ishi_projection_output_dim(const ishi_projection *p); /* Projection.outputDim */

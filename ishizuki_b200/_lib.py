@@ -44,6 +44,7 @@ SIGNATURES = {
     "ishi_ctx_set_route": (c_int, [c_void_p, c_int, c_int]),
     "ishi_projection_create": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(c_void_p)]),
     "ishi_projection_create_fused": (c_int, [c_void_p, POINTER(WeightDesc), c_int, POINTER(c_void_p)]),
+    "ishi_projection_create_gated": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(WeightDesc), POINTER(c_void_p)]),
     "ishi_projection_destroy": (None, [c_void_p]),
     "ishi_projection_input_dim": (c_int64, [c_void_p]),
     "ishi_projection_output_dim": (c_int64, [c_void_p]),

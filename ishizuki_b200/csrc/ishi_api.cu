@@ -99,6 +99,7 @@ struct ishi_projection {
   RowPlan plan;          // tcgen05 kernel (formats without a fragment decoder)
   FragPlan frag;         // warp-level kernel
   bool generic = false;  // neither: the one-warp-per-row kernel reads a plain copy of the blocks (ws.tiles)
+  bool gated = false;    // gate and up interleaved by eights, the kernel's epilogue writes silu(gate) * up: d.n / 2 output rows
   __half *logits = nullptr;  // [16][n] of apply_argmax, allocated by its first call
   Workspace ws;          // this projection's own scratch and tiled weight: apply never allocates
   __half *xr = nullptr;  // rotated activations [16][k] when the pack is rotated
@@ -107,6 +108,9 @@ struct ishi_projection {
 };
 
 namespace {
+
+// output rows the caller sees
+int64_t out_rows(const ishi_projection *p) { return p->gated ? p->d.n / 2 : p->d.n; }
 
 ishi_status fail(ishi_ctx *ctx, ishi_status s, const char *fmt, ...) {
   if (ctx) {
@@ -496,9 +500,10 @@ bool make_frag_plan(ishi_ctx *ctx, const ishi_weight_desc &d, FragPlan *pl, std:
 }
 
 ishi_status tile_weight_frag(ishi_ctx *ctx, const FragPlan &pl, const ishi_weight_desc *parts, int count, long long n_total,
-                             uint8_t *dst, cudaStream_t st) {
+                             uint8_t *dst, cudaStream_t st, bool pair_rows = false) {
   FragSrc src;
   memset(&src, 0, sizeof(src));
+  src.pair_rows = pair_rows ? 1 : 0;
   const ishi_weight_desc &d = parts[0];
   src.N = n_total;
   src.segments = count;
@@ -551,7 +556,7 @@ bool single_row_on_cuda_cores(const ishi_ctx *ctx) {
 // rows 1...16 through the warp-level kernel; gemv picks the CUDA-core variant for a single row
 ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, const ishi_weight_desc &d, const void *x,
                      int rows, void *y, long long ldy, int flags, bool gemv, bool early, bool rotate, cudaStream_t st,
-                     const PeerOut *peers = nullptr) {
+                     const PeerOut *peers = nullptr, bool gated = false) {
   for (int r0 = 0; r0 < rows; r0 += 8) {
     FragArgs a;
     memset(&a, 0, sizeof(a));
@@ -581,6 +586,7 @@ ishi_status run_frag(ishi_ctx *ctx, const FragPlan &pl, const Workspace &ws, con
     a.err = ctx->err_dev;
     a.rot_block = rotate ? d.hadamard_block : 0;
     a.rot_signs = rotate ? static_cast<const float *>(d.signs_dev) : nullptr;
+    a.swiglu = gated ? 1 : 0;
 #ifdef ISHI_TRACE
     a.trace = g_trace;
 #endif
@@ -680,12 +686,12 @@ ishi_status projection_matmul(ishi_projection *p, const void *x, int rows, void 
   ishi_ctx *ctx = p->ctx;
   ishi_status s = check_io(ctx, x, rows, y, 16);
   if (s != ISHI_OK) return s;
-  const int64_t need_ld = (flags & ISHI_OUT_TRANSPOSED) ? rows : p->d.n;
+  const int64_t need_ld = (flags & ISHI_OUT_TRANSPOSED) ? rows : out_rows(p);
   if (ldy < need_ld) return fail(ctx, ISHI_E_SHAPE, "ldy %lld shorter than %lld", (long long)ldy, (long long)need_ld);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   if (p->frag.ok)
     return run_frag(ctx, p->frag, p->ws, p->d, x, rows, y, ldy, flags, single_row_on_cuda_cores(ctx),
-                    getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, rotate, st);
+                    getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, rotate, st, nullptr, p->gated);
   if (p->generic) {
     if (rotate) return fail(ctx, ISHI_E_INVALID, "in-kernel rotation asked of a kernel that has none");
     ISHI_CUDA(ctx, launch_ggml_rowdot(p->d.ggml_type, p->ws.tiles, p->d.n, p->d.k, static_cast<const __half *>(x), rows,
@@ -975,8 +981,8 @@ static void tune_frag_plan(ishi_ctx *ctx, ishi_projection *p, std::vector<FragPl
   if (y) cudaFree(y);
 }
 
-ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
-                                         ishi_projection **out) {
+static ishi_status create_projection(ishi_ctx *ctx, const ishi_weight_desc *descs, int count, bool gated,
+                                     ishi_projection **out) {
   if (!ctx || !out) return ISHI_E_INVALID;
   *out = nullptr;
   if (!descs) return fail(ctx, ISHI_E_INVALID, "null descriptor");
@@ -994,13 +1000,16 @@ ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *
     wb += part;
     n_total += b.n;
   }
+  if (gated && (count != 2 || descs[0].n != descs[1].n || (descs[0].n & 7)))
+    return fail(ctx, ISHI_E_SHAPE, "a gated pair needs two weights of the same height, a multiple of 8");
   std::lock_guard<std::mutex> g(ctx->lock);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   ishi_projection *p = new (std::nothrow) ishi_projection();
   if (!p) return fail(ctx, ISHI_E_NOMEM, "out of host memory");
   p->ctx = ctx;
   p->d = descs[0];
-  p->d.n = n_total;  // the projection's output rows: the weights stacked in the order given
+  p->d.n = n_total;  // the projection's weight rows: the weights stacked in the order given
+  p->gated = gated;  // (or interleaved by eights, see FragSrc::pair_rows)
   p->fmt = format_of(descs[0]);
   p->weight_bytes = wb;
   ishi_status s = ISHI_OK;
@@ -1009,7 +1018,7 @@ ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *
   std::vector<FragPlan> candidates;
   if (make_frag_plan(ctx, p->d, &p->frag, &candidates)) {
     s = ensure_workspace(ctx, &p->ws, 0, 0, p->frag.tiles_bytes, 0);
-    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, descs, count, n_total, p->ws.tiles, 0);
+    if (s == ISHI_OK) s = tile_weight_frag(ctx, p->frag, descs, count, n_total, p->ws.tiles, 0, gated);
     if (s == ISHI_OK && !getenv("ISHI_NO_AUTOTUNE") && !getenv("ISHI_FRAG_PLAN")) tune_frag_plan(ctx, p, &candidates);
   } else if (count > 1) {
     delete p;
@@ -1047,8 +1056,22 @@ ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *
   return ISHI_OK;
 }
 
+ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
+                                         ishi_projection **out) {
+  return create_projection(ctx, descs, count, false, out);
+}
+
+ishi_status ishi_projection_create_gated(ishi_ctx *ctx, const ishi_weight_desc *gate, const ishi_weight_desc *up,
+                                         ishi_projection **out) {
+  if (!ctx || !out) return ISHI_E_INVALID;
+  *out = nullptr;
+  if (!gate || !up) return fail(ctx, ISHI_E_INVALID, "null descriptor");
+  const ishi_weight_desc pair[2] = {*gate, *up};
+  return create_projection(ctx, pair, 2, true, out);
+}
+
 ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc, ishi_projection **out) {
-  return ishi_projection_create_fused(ctx, desc, 1, out);
+  return create_projection(ctx, desc, 1, false, out);
 }
 
 void ishi_projection_destroy(ishi_projection *p) {
@@ -1063,7 +1086,7 @@ void ishi_projection_destroy(ishi_projection *p) {
 }
 
 int64_t ishi_projection_input_dim(const ishi_projection *p) { return p ? p->d.k : 0; }
-int64_t ishi_projection_output_dim(const ishi_projection *p) { return p ? p->d.n : 0; }
+int64_t ishi_projection_output_dim(const ishi_projection *p) { return p ? out_rows(p) : 0; }
 int64_t ishi_projection_weight_bytes(const ishi_projection *p) { return p ? p->weight_bytes : 0; }
 int ishi_projection_crossover_rows(const ishi_projection *p) {
   if (!p) return 0;
@@ -1140,13 +1163,13 @@ ishi_status ishi_projection_apply_argmax(ishi_projection *p, const void *x, int 
     std::lock_guard<std::mutex> g(ctx->lock);
     if (!p->logits) {
       __half *l = nullptr;
-      if (cudaMalloc(&l, (size_t)16 * p->d.n * sizeof(__half)) != cudaSuccess) return fail(ctx, ISHI_E_NOMEM, "logits buffer");
+      if (cudaMalloc(&l, (size_t)16 * out_rows(p) * sizeof(__half)) != cudaSuccess) return fail(ctx, ISHI_E_NOMEM, "logits buffer");
       p->logits = l;
     }
   }
-  ishi_status s = ishi_projection_apply(p, x, rows, p->logits, p->d.n, 0, stream);
+  ishi_status s = ishi_projection_apply(p, x, rows, p->logits, out_rows(p), 0, stream);
   if (s != ISHI_OK) return s;
-  ISHI_CUDA(ctx, launch_argmax_rows(p->logits, rows, p->d.n, p->d.n, argmax_dev, static_cast<cudaStream_t>(stream)));
+  ISHI_CUDA(ctx, launch_argmax_rows(p->logits, rows, out_rows(p), out_rows(p), argmax_dev, static_cast<cudaStream_t>(stream)));
   return ISHI_OK;
 }
 
@@ -1165,9 +1188,9 @@ ishi_status ishi_projection_apply_host_async(ishi_projection *p, const void *x_h
     ishi_status s0 = ensure_host_staging(p);
     if (s0 != ISHI_OK) return s0;
   }
-  const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * p->d.n * sizeof(__half);
+  const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * out_rows(p) * sizeof(__half);
   ISHI_CUDA(ctx, cudaMemcpyAsync(p->host_x, x_host, xb, cudaMemcpyHostToDevice, st));
-  ishi_status s = ishi_projection_apply(p, p->host_x, rows, p->host_y, p->d.n, 0, stream);
+  ishi_status s = ishi_projection_apply(p, p->host_x, rows, p->host_y, out_rows(p), 0, stream);
   if (s != ISHI_OK) return s;
   ISHI_CUDA(ctx, cudaMemcpyAsync(y_host, p->host_y, yb, cudaMemcpyDeviceToHost, st));
   return ISHI_OK;
@@ -1181,7 +1204,7 @@ static ishi_status ensure_host_staging(ishi_projection *p) {
   if (p->host_x) return ISHI_OK;
   __half *hx = nullptr, *hy = nullptr;
   ISHI_CUDA(ctx, cudaMalloc(&hx, (size_t)16 * p->d.k * sizeof(__half)));
-  cudaError_t e = cudaMalloc(&hy, (size_t)16 * p->d.n * sizeof(__half));
+  cudaError_t e = cudaMalloc(&hy, (size_t)16 * out_rows(p) * sizeof(__half));
   if (e != cudaSuccess) {
     cudaFree(hx);
     return fail(ctx, ISHI_E_NOMEM, "device staging: %s", cudaGetErrorString(e));
@@ -1241,13 +1264,13 @@ ishi_status ishi_projection_apply_host_batch(ishi_projection *const *ps, const v
     ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_in[c0], ctx->copy_in));
     ISHI_CUDA(ctx, cudaStreamWaitEvent(st, ctx->ev_in[c0], 0));
     for (int i = c0; i < c1; ++i) {
-      ishi_status s = ishi_projection_apply(ps[i], ps[i]->host_x, rows, ps[i]->host_y, ps[i]->d.n, 0, stream);
+      ishi_status s = ishi_projection_apply(ps[i], ps[i]->host_x, rows, ps[i]->host_y, out_rows(ps[i]), 0, stream);
       if (s != ISHI_OK) return s;
     }
     ISHI_CUDA(ctx, cudaEventRecord(ctx->ev_done[c0], st));
     ISHI_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[c0], 0));
     for (int i = c0; i < c1; ++i) {
-      const size_t yb = (size_t)rows * ps[i]->d.n * sizeof(__half);
+      const size_t yb = (size_t)rows * out_rows(ps[i]) * sizeof(__half);
       ISHI_CUDA(ctx, cudaMemcpyAsync(y_hosts[i], ps[i]->host_y, yb, cudaMemcpyDeviceToHost, ctx->copy_out));
     }
   }
@@ -1262,7 +1285,7 @@ ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, i
   if (!x_host || !y_host) return fail(ctx, ISHI_E_INVALID, "null pointer");
   if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * p->d.n * sizeof(__half);
+  const size_t xb = (size_t)rows * p->d.k * sizeof(__half), yb = (size_t)rows * out_rows(p) * sizeof(__half);
   {
     std::lock_guard<std::mutex> g(ctx->lock);
     ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -1281,7 +1304,7 @@ ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, i
       if (ctx->dev_y) cudaFree(ctx->dev_y);
       ctx->pin_y = ctx->dev_y = nullptr;
       ctx->pin_y_bytes = 0;
-      const size_t cap = (size_t)16 * p->d.n * sizeof(__half);
+      const size_t cap = (size_t)16 * out_rows(p) * sizeof(__half);
       ISHI_CUDA(ctx, cudaHostAlloc(&ctx->pin_y, cap, cudaHostAllocDefault));
       ISHI_CUDA(ctx, cudaMalloc(&ctx->dev_y, cap));
       ctx->pin_y_bytes = cap;
@@ -1289,7 +1312,7 @@ ishi_status ishi_projection_apply_host(ishi_projection *p, const void *x_host, i
   }
   memcpy(ctx->pin_x, x_host, xb);
   ISHI_CUDA(ctx, cudaMemcpyAsync(ctx->dev_x, ctx->pin_x, xb, cudaMemcpyHostToDevice, st));
-  ishi_status s = ishi_projection_apply(p, ctx->dev_x, rows, ctx->dev_y, p->d.n, 0, stream);
+  ishi_status s = ishi_projection_apply(p, ctx->dev_x, rows, ctx->dev_y, out_rows(p), 0, stream);
   if (s != ISHI_OK) return s;
   ISHI_CUDA(ctx, cudaMemcpyAsync(ctx->pin_y, ctx->dev_y, yb, cudaMemcpyDeviceToHost, st));
   ISHI_CUDA(ctx, cudaStreamSynchronize(st));
@@ -1426,9 +1449,9 @@ ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const voi
   if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
   const size_t row_bytes = rows > 8 ? 32 : 16;
   if (out_offset_bytes < 0 || (out_offset_bytes & 15) || row_offset < 0 ||
-      (size_t)out_offset_bytes + (size_t)(row_offset + p->d.n) * row_bytes > ex->bytes)
+      (size_t)out_offset_bytes + (size_t)(row_offset + out_rows(p)) * row_bytes > ex->bytes)
     return fail(ctx, ISHI_E_SHAPE, "rows %lld...%lld at offset %lld do not fit the exchange buffer", (long long)row_offset,
-                (long long)(row_offset + p->d.n), (long long)out_offset_bytes);
+                (long long)(row_offset + out_rows(p)), (long long)out_offset_bytes);
   const int b = p->d.hadamard_block;
   if (b != 0 && !rotates_in_kernel(p)) return fail(ctx, ISHI_E_UNSUPPORTED, "rotation block %d needs its own kernel", b);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -1446,7 +1469,7 @@ ishi_status ishi_exchange_apply(ishi_exchange *ex, ishi_projection *p, const voi
   po.wait_previous = wait_previous ? 1 : 0;
   po.row_offset = row_offset;
   return run_frag(ctx, p->frag, p->ws, p->d, x, rows, ex->buf + out_offset_bytes, rows > 8 ? 16 : 8, ISHI_OUT_TRANSPOSED, false,
-                  getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, b != 0, static_cast<cudaStream_t>(stream), &po);
+                  getenv("ISHI_NO_EARLY_LAUNCH") == nullptr, b != 0, static_cast<cudaStream_t>(stream), &po, p->gated);
 }
 
 ishi_status ishi_exchange_wait(ishi_exchange *ex, void *stream) {

@@ -76,6 +76,9 @@ struct FragArgs {
   // Block Hadamard rotation of x while it is staged (0: none): xr = WHT_block(x * signs) / sqrt(block)
   int rot_block;           // a power of two, 8 ... 256
   const float *rot_signs;  // [K] or null
+  // Gated pair (the weight was tiled with FragSrc::pair_rows): rows g and g + 8 of a panel are the
+  // gate and the up row of output row 8 p + g, and the epilogue writes silu(gate) * up, N / 2 rows
+  int swiglu;
   // Output exchange between the GPUs of an N-sharded projection (world = 0: none). Every rank holds
   // the whole output as [rows of all shards][8 or 16] fp16 at the same place of its exchange buffer; this
   // launch computes rows row_offset ... row_offset + N - 1 and stores them into every rank's copy
@@ -204,6 +207,17 @@ __device__ __forceinline__ void st_relaxed_sys(unsigned *p, unsigned v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// silu(gate) * up as the reference's MLP computes it on fp16 arrays (downProj(silu(gateProj(x)) *
+// upProj(x)), Sources/IshizukiKit/Text/Attention.swift:251): the two products rounded to fp16,
+// sigmoid, gate * sigmoid and the product with up each rounded to fp16 (one array per operation),
+// the arithmetic itself in fp32. Returns the fp16 value as a float.
+__device__ __forceinline__ float frag_swiglu(float gate, float up) {
+  const float gf = __half2float(__float2half_rn(gate)), uf = __half2float(__float2half_rn(up));
+  const float sig = __half2float(__float2half_rn(1.0f / (1.0f + expf(-gf))));
+  const float act = __half2float(__float2half_rn(gf * sig));
+  return __half2float(__float2half_rn(act * uf));
+}
+
 // One lane's part of panel p's finished 16 x 8 tile, in accumulator-fragment order: lane
 // (g = lane / 4, t = lane % 4) holds v.x, v.y = weight row g, activation rows 2t, 2t + 1 and
 // v.z, v.w = weight row g + 8, the same activation rows. Called by all 32 lanes of a warp.
@@ -212,6 +226,32 @@ __device__ __forceinline__ void st_relaxed_sys(unsigned *p, unsigned v) {
 __device__ __forceinline__ void frag_write(const FragArgs &a, int p, int lane, float4 v) {
   const int g = lane >> 2, t = lane & 3;
   const long long n0 = (long long)p * kFragRows + g;
+  if (a.swiglu) {
+    // v.x, v.y: the gate row, v.z, v.w: the up row of output row 8 p + g
+    v.x = frag_swiglu(v.x, v.z), v.y = frag_swiglu(v.y, v.w);
+    const long long n = (long long)p * 8 + g;
+    if (a.world > 0) {
+      const __half2 h = __floats2half2_rn(v.x, v.y);
+      const uint32_t ph = *reinterpret_cast<const uint32_t *>(&h);
+      const int base = lane & ~3;
+      uint4 row;
+      row.x = __shfl_sync(0xffffffffu, ph, base), row.y = __shfl_sync(0xffffffffu, ph, base + 1);
+      row.z = __shfl_sync(0xffffffffu, ph, base + 2), row.w = __shfl_sync(0xffffffffu, ph, base + 3);
+      if (n < a.N / 2 && t < 2)  // lanes t = 0, 1 store to the even / odd ranks
+        for (int q = t; q < a.world; q += 2) *reinterpret_cast<uint4 *>(a.peer_y[q] + (a.row_offset + n) * a.peer_ld) = row;
+      return;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int m = 2 * t + i;
+      if (n < a.N / 2 && m < a.M) {
+        const __half h = __float2half_rn(i ? v.y : v.x);
+        if (a.out_transposed) a.y[n * a.ldy + m] = h;
+        else a.y[(long long)m * a.ldy + n] = h;
+      }
+    }
+    return;
+  }
   if (a.world > 0) {
     const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
     const uint32_t plo = *reinterpret_cast<const uint32_t *>(&lo), phi = *reinterpret_cast<const uint32_t *>(&hi);
@@ -672,10 +712,18 @@ struct FragSrc {
   long long w_row_bytes, s_row_bytes;  // distance between rows
   long long N;
   int group_size, scale_bytes;
+  // Two segments of equal height interleaved by eights instead of stacked: rows 0-7 of panel p are
+  // rows 8 p ... 8 p + 7 of segment 0, rows 8-15 the same rows of segment 1, so that one
+  // accumulator fragment holds a row of each (see FragArgs::swiglu).
+  int pair_rows;
 };
 
 // which segment holds output row `row` (< N), and the row's index inside it
 __device__ __forceinline__ int frag_segment(const FragSrc &s, long long row, long long *local) {
+  if (s.pair_rows) {
+    *local = (row >> 4) * 8 + (row & 7);
+    return (int)(row >> 3) & 1;
+  }
   int i = 0;
   while (i + 1 < s.segments && row >= s.first_row[i + 1]) ++i;
   *local = row - s.first_row[i];

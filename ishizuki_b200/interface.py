@@ -439,9 +439,16 @@ class FusedLinear(PackedLinear):
     (Attention.swift:251) as separate kernels on the same input; here their weights are stacked
     along the output rows at create time and one launch streams them all. ``parts`` is a list of
     GGUFBlocks (same type and input width) or of (weight, scales, biases) affine packs (same
-    width, group size and scale dtype). ``split(y)`` gives the parts' outputs back as views."""
+    width, group size and scale dtype). ``split(y)`` gives the parts' outputs back as views.
 
-    def __init__(self, parts, signs=None, block: int = 0, groupSize: int = 128, bits: int = 2):  # noqa: N803
+    ``gated=True`` takes exactly two parts, the MLP's gate and up projections, and makes the
+    launch's output ``silu(x . gate^T) * (x . up^T)`` (the input of the reference's downProj,
+    Attention.swift:251): the rows of the two weights are interleaved by eights at create time so
+    that one accumulator fragment holds a gate row and its up row, and the kernel's epilogue
+    combines them. ``outputDim`` is then the height of one part."""
+
+    def __init__(self, parts, signs=None, block: int = 0, groupSize: int = 128, bits: int = 2,  # noqa: N803
+                 gated: bool = False):
         first = parts[0]
         self.signs, self.block = signs, block
         if isinstance(first, GGUFBlocks):
@@ -465,13 +472,23 @@ class FusedLinear(PackedLinear):
         for i, (w, s, b) in enumerate(triples):
             descs[i] = self._describe(w, s, b, self.outputDims[i])
         handle = ctypes.c_void_p()
-        rc = self.ctx.lib.ishi_projection_create_fused(self.ctx.handle, descs, len(triples), ctypes.byref(handle))
+        self.gated = gated
+        if gated:
+            if len(triples) != 2:
+                raise ValueError("a gated pair is two weights: gate and up")
+            rc = self.ctx.lib.ishi_projection_create_gated(self.ctx.handle, ctypes.byref(descs[0]), ctypes.byref(descs[1]),
+                                                           ctypes.byref(handle))
+            self.outputDim = self.outputDims[0]
+        else:
+            rc = self.ctx.lib.ishi_projection_create_fused(self.ctx.handle, descs, len(triples), ctypes.byref(handle))
         if rc != _lib.OK:
             raise IshizukiError(rc, self.ctx.last_error())
         self.handle = handle
         self.weight = self.scales = self.biases = None  # the library keeps its own tiled copy
 
     def split(self, y: torch.Tensor, transposed: bool = False):
+        if self.gated:
+            raise ValueError("a gated pair has one output: silu(gate) * up")
         return torch.split(y, self.outputDims, dim=0 if transposed else -1)
 
 

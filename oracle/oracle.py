@@ -125,6 +125,20 @@ def affine_dequantize(w: np.ndarray, scales: np.ndarray, biases: np.ndarray, bit
     return out
 
 
+def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """silu(gate) * up on fp16 arrays, the input of the reference's downProj
+    (Sources/IshizukiKit/Text/Attention.swift:251: downProj(silu(gateProj(x)) * upProj(x))). Each
+    element-wise operation of the reference yields an fp16 array, so sigmoid, gate * sigmoid and the
+    product with up are each rounded to fp16; the arithmetic in between is fp32. The reference
+    holds no vector for this stage (it runs through MLX): pinned by the formula only."""
+    assert gate.dtype == np.float16 and up.dtype == np.float16
+    g = gate.astype(np.float32)
+    with np.errstate(over="ignore"):
+        sig = (np.float32(1) / (np.float32(1) + np.exp(-g))).astype(np.float16).astype(np.float32)
+    act = (g * sig).astype(np.float16).astype(np.float32)
+    return (act * up.astype(np.float32)).astype(np.float16)
+
+
 def hadamard_rotate(x: np.ndarray, block: int, signs: np.ndarray | None = None) -> np.ndarray:
     """Block Hadamard rotation of fp16 rows, fp32 inside, fp16 out."""
     assert x.dtype == np.float16

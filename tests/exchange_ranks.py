@@ -29,14 +29,17 @@ def main() -> None:
     dist.init_process_group("gloo")  # the host side only passes handles around
     rng = np.random.default_rng(11)  # the same weights on every rank
     # (rows of every matrix of the launch, k); rows divide by 8 ranks
-    launches = [((2048,), 1024), ((1024, 512, 512), 2048), ((4096, 4096), 1024), ((640,), 4352)]
+    # a third entry marks gate / up as a gated pair: silu(gate) * up, sharded along its own rows
+    launches = [((2048,), 1024), ((1024, 512, 512), 2048), ((4096, 4096), 1024), ((640,), 4352), ((1024, 1024), 2048, "gated")]
     ex = OutputExchange(4 << 20)
     cases = []
-    for sizes, k in launches:
+    for sizes, k, *kind in launches:
         mats = [synth.q4k_blocks(rng, n, k) for n in sizes]
 
         def build(q):
             parts = [shard(b, n, k, q, world) for b, n in zip(mats, sizes)]
+            if kind:
+                return FusedLinear(parts, gated=True)
             return FusedLinear(parts) if len(parts) > 1 else PackedLinear(ggml=parts[0])
 
         local = build(rank)

@@ -304,6 +304,90 @@ def test_a_projection_under_another_ones_plan_gives_the_same_bits():
         b.set_plan((2, 25, 8, 3))  # more warps than a block holds: not a plan of this projection
 
 
+def _check_gated(gated, stacked, x, want_gate, want_up):
+    """The gated launch against (a) the oracle's silu(gate) * up on the oracle's fp16 products and
+    (b) the same formula on this library's own stacked products, which differ from the kernel's
+    only where the device's exp rounds another way: a unit in the last place, rarely."""
+    f = gated.outputDim
+    h = gated(dev(x))
+    torch.cuda.synchronize()
+    gated.ctx.poll()
+    assert h.shape == (x.shape[0], f)
+    want = oracle.swiglu(want_gate, want_up).astype(np.float32)
+    assert rel_err(h.cpu().numpy().astype(np.float32), want) < TOL
+    gate_y, up_y = stacked.split(stacked(dev(x)))
+    own = oracle.swiglu(gate_y.cpu().numpy(), up_y.cpu().numpy())
+    got = h.cpu().numpy()
+    differing = got.view(np.uint16) != own.view(np.uint16)
+    assert differing.mean() < 1e-3
+    assert np.all(np.abs(got.astype(np.float32) - own.astype(np.float32))[differing] <= np.abs(own.astype(np.float32))[differing] * 2.0 ** -9 + 1e-7)
+
+
+@pytest.mark.parametrize("f,k", [(17408, 5120), (1000, 1024), (8, 512)])
+def test_gated_pair_writes_silu_gate_times_up(f, k):
+    """ishi_projection_create_gated: gate and up interleaved by eights in the tiled copy, the
+    kernel's epilogue writes silu(x . gate^T) * (x . up^T), [rows, f]."""
+    rng = np.random.default_rng(f + k)
+    gate, up = synth.q4k_blocks(rng, f, k), synth.q4k_blocks(rng, f, k)
+    parts = [GGUFBlocks(dev(gate), GGMLType.q4K, (f, k)), GGUFBlocks(dev(up), GGMLType.q4K, (f, k))]
+    gated = FusedLinear(parts, gated=True)
+    stacked = FusedLinear(parts)
+    stacked.set_plan(gated.plan)  # the same order of partial sums
+    assert gated.outputDim == f and stacked.outputDim == 2 * f
+    for m in (1, 8, 11):
+        x = synth.activations(rng, m, k)
+        _, g16 = oracle.ggml_matmul(int(GGMLType.q4K), gate, x, f)
+        _, u16 = oracle.ggml_matmul(int(GGMLType.q4K), up, x, f)
+        _check_gated(gated, stacked, x, g16, u16)
+
+
+def test_gated_pair_other_formats_and_a_single_row_on_cuda_cores():
+    rng = np.random.default_rng(77)
+    f, k = 264, 2048
+    x = synth.activations(rng, 8, k)
+    packs = [synth.affine_pack(rng, f, k, 4, 64, np.float16) for _ in range(2)]
+    parts = [(dev(w), dev(s), dev(b)) for w, s, b in packs]
+    gated, stacked = FusedLinear(parts, groupSize=64, bits=4, gated=True), FusedLinear(parts, groupSize=64, bits=4)
+    stacked.set_plan(gated.plan)
+    wants = [oracle.affine_matmul(w, s, b, 4, 64, x)[1] for w, s, b in packs]
+    _check_gated(gated, stacked, x, *wants)
+    blocks = [synth.q6k_blocks(rng, f, k) for _ in range(2)]
+    parts = [GGUFBlocks(dev(b), GGMLType.q6K, (f, k)) for b in blocks]
+    gated, stacked = FusedLinear(parts, gated=True), FusedLinear(parts)
+    stacked.set_plan(gated.plan)
+    wants = [oracle.ggml_matmul(int(GGMLType.q6K), b, x, f)[1] for b in blocks]
+    _check_gated(gated, stacked, x, *wants)
+    # one row through the CUDA-core route
+    blocks = [synth.q4k_blocks(rng, f, k) for _ in range(2)]
+    parts = [GGUFBlocks(dev(b), GGMLType.q4K, (f, k)) for b in blocks]
+    gated = FusedLinear(parts, gated=True)
+    x1 = synth.activations(rng, 1, k)
+    wants = [oracle.ggml_matmul(int(GGMLType.q4K), b, x1, f)[1] for b in blocks]
+    want = oracle.swiglu(*wants).astype(np.float32)
+    BonsaiRuntime.route = _lib.ROUTE_GEMV
+    try:
+        h = gated(dev(x1))
+    finally:
+        BonsaiRuntime.route = _lib.ROUTE_AUTO
+    assert rel_err(h.cpu().numpy().astype(np.float32), want) < TOL
+    gated.ctx.poll()
+
+
+def test_gated_pair_guards():
+    rng = np.random.default_rng(3)
+    a = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 512)), GGMLType.q4K, (32, 512))
+    b = GGUFBlocks(dev(synth.q4k_blocks(rng, 40, 512)), GGMLType.q4K, (40, 512))
+    c = GGUFBlocks(dev(synth.q4k_blocks(rng, 20, 512)), GGMLType.q4K, (20, 512))
+    with pytest.raises(IshizukiError) as err:
+        FusedLinear([a, b], gated=True)  # different heights
+    assert err.value.status == _lib.E_SHAPE
+    with pytest.raises(IshizukiError) as err:
+        FusedLinear([c, c], gated=True)  # height not a multiple of 8
+    assert err.value.status == _lib.E_SHAPE
+    with pytest.raises(ValueError):
+        FusedLinear([a, a, a], gated=True)
+
+
 def test_stacking_guards():
     rng = np.random.default_rng(2)
     a = GGUFBlocks(dev(synth.q4k_blocks(rng, 32, 512)), GGMLType.q4K, (32, 512))
