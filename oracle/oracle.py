@@ -217,3 +217,91 @@ def read_ggml_fixture(path) -> dict[int, tuple[np.ndarray, np.ndarray]]:
         cur += 4 * nf
         out[tid] = (blocks, want)
     return out
+
+# ---- EXL3 trellis-coded weights (reference: Sources/IshizukiKit/Core/EXL3.swift) ----------------
+#
+# A 16 x 16 tile of W [k, n] is one ring of 256 * bits bits (half-integer rates: 128 * (2 * whole + 1)),
+# stored as 16 * bits int16 (read as 32-bit little-endian words, bits counted from each word's top).
+# Weight p of the tile (0...255) is a function of the 16 ring bits that end where p's own code ends
+# (EXL3.swift:184-186, 200-214); the function is one of three procedural codebooks
+# (EXL3.swift:171-182). Weight p = 8 * lane + i sits at row (lane % 4) * 2 + {0, 1, 8, 9}[i % 4],
+# column lane / 4 + 8 * (i / 4) of the tile (EXL3.swift:286-290): the layout of a 16 x 8 x 16
+# matrix-multiply fragment.
+EXL3_3INST, EXL3_MCG, EXL3_MUL1 = 0, 1, 2
+
+
+def _exl3_codes_end(whole: int, half: bool) -> np.ndarray:
+    p = np.arange(256)
+    if half:
+        return (p >> 1) * (2 * whole + 1) + whole + (p & 1) * (whole + 1)
+    return (p + 1) * whole
+
+
+def _bits_to_half(bits: np.ndarray) -> np.ndarray:
+    return bits.astype(np.uint16).view(np.float16)
+
+
+def exl3_decode(state: np.ndarray, codebook: int) -> np.ndarray:
+    """The weight of a 16-bit trellis state, as float32 (EXL3.swift:171-182). All values are fp16
+    numbers: the codebooks end in one fp16 operation (an add, or a fused multiply-add)."""
+    s = state.astype(np.uint64)
+    if codebook == EXL3_MUL1:
+        x = (s * 0x83DCD12D) & 0xFFFFFFFF
+        p = (x & 0x00FF00FF) + ((x >> 8) & 0x00FF00FF)
+        h = _bits_to_half((p & 0xFFFF) + (p >> 16) + 0x6400).astype(np.float64)
+        a = float(_bits_to_half(np.array([0x1EEE]))[0])
+        b = float(_bits_to_half(np.array([0xC931]))[0])
+        return (h * a + b).astype(np.float16).astype(np.float32)  # exact in float64, rounded once
+    x = (s * 0xCBAC1FED) & 0xFFFFFFFF if codebook == EXL3_MCG else (s * 89226354 + 64248484) & 0xFFFFFFFF
+    x = (x & 0x8FFF8FFF) ^ 0x3B603B60
+    lo, hi = _bits_to_half(x & 0xFFFF).astype(np.float64), _bits_to_half(x >> 16).astype(np.float64)
+    return (lo + hi).astype(np.float16).astype(np.float32)
+
+
+def exl3_dequantize(trellis: np.ndarray, codebook: int) -> np.ndarray:
+    """int16 [k / 16, n / 16, 16 * bits] -> float32 W [k, n] (EXL3.swift:275-292)."""
+    assert trellis.dtype == np.int16 and trellis.ndim == 3
+    tk, tn, words16 = trellis.shape
+    whole, half = words16 // 16, words16 % 16 != 0
+    assert words16 in (16 * whole, 16 * whole + 8)
+    ring = 16 * words16
+    words = np.ascontiguousarray(trellis).view(np.uint32).reshape(tk * tn, ring // 32)
+    # the ring as bits, each 32-bit word from its top bit down
+    bits = np.unpackbits(words.byteswap().view(np.uint8).reshape(tk * tn, ring // 8), axis=1)
+    end = _exl3_codes_end(whole, half)
+    idx = (end[:, None] - 16 + np.arange(16)[None, :]) % ring                 # [256, 16]
+    state = (bits[:, idx].astype(np.uint32) << (15 - np.arange(16, dtype=np.uint32))).sum(axis=2)  # [tiles, 256]
+    v = exl3_decode(state, codebook)
+    lane, i = np.arange(256) // 8, np.arange(256) % 8
+    row = (lane % 4) * 2 + np.array([0, 1, 8, 9])[i % 4]
+    col = lane // 4 + 8 * (i // 4)
+    tiles = np.empty((tk * tn, 16, 16), dtype=np.float32)
+    tiles[:, row, col] = v
+    return tiles.reshape(tk, tn, 16, 16).transpose(0, 2, 1, 3).reshape(tk * 16, tn * 16)
+
+
+def exl3_rotate(x: np.ndarray, scales: np.ndarray, before: bool, dtype=np.float16) -> np.ndarray:
+    """Block Hadamard of 128 with a scale vector on the input (before) or the output side, fp32
+    inside (EXL3.swift:114-122, 219-262)."""
+    rows, width = x.shape
+    h = x.astype(np.float32)
+    s = scales.astype(np.float32)
+    if before:
+        h = h * s
+    hm = np.array([[1.0]], dtype=np.float32)
+    while hm.shape[0] < 128:
+        hm = np.block([[hm, hm], [hm, -hm]])
+    h = (h.reshape(-1, 128).astype(np.float64) @ hm.astype(np.float64)).astype(np.float32) * np.float32(0.08838834764831845)
+    h = h.reshape(rows, width)
+    if not before:
+        h = h * s
+    return h.astype(dtype)
+
+
+def exl3_apply(x: np.ndarray, trellis: np.ndarray, input_scales: np.ndarray, output_scales: np.ndarray, codebook: int):
+    """EXL3Kernels.apply (EXL3.swift:83-106): rotate x (scales first) to fp16, multiply by the
+    decoded W in fp32, rotate the fp32 product (scales last) to fp16."""
+    xh = exl3_rotate(x, input_scales, True, np.float16)
+    w = exl3_dequantize(trellis, codebook).astype(np.float64)
+    yh = (xh.astype(np.float64) @ w).astype(np.float32)
+    return exl3_rotate(yh, output_scales, False, np.float16)

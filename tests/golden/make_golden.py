@@ -13,6 +13,13 @@ reference tree is not present where the GPU tests run.
                         block-1024 rotated form, plus the +-1 sign vector recovered from them
                         (the pack's own sign tensor is not in the reference tree).
 
+  exl3_reference.npz    every array of Tests/IshizukiKitTests/Fixtures/exl3-reference.safetensors:
+                        eleven EXL3 trellis tensors "r<bits>[h5]c<codebook>" (int16 [k/16, n/16,
+                        16 * bits]) with the exllamav3 reconstruction of each ("expected", fp32
+                        [k, n]), and one projection of two checkpoints ("qwen3": codebook 3INST,
+                        "qwen38": mul1) with trellis, input / output scale vectors and the fp16
+                        weight it was quantized from.
+
 Usage: python tests/golden/make_golden.py /path/to/reference
 """
 import pathlib
@@ -51,6 +58,11 @@ def main() -> None:
     np.savez_compressed(here / "hadamard_case1.npz", x=x, rotated=h, signs=signs,
                         block=np.int32(block))
     print("negatives in sign vector:", int((signs < 0).sum()))
+
+    with safe_open(str(ref / "Tests/IshizukiKitTests/Fixtures/exl3-reference.safetensors"), "np") as f:
+        arrays = {name: f.get_tensor(name) for name in f.keys()}
+    np.savez_compressed(here / "exl3_reference.npz", **arrays)
+    print("EXL3 arrays:", len(arrays))
 
 
 if __name__ == "__main__":

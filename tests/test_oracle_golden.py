@@ -95,3 +95,45 @@ def test_matmul_agrees_with_numpy():
     want = x.astype(np.float64) @ w.astype(np.float64).T
     assert np.abs(y32 - want).max() <= 1e-6 * np.abs(want).max()
     assert np.array_equal(y16, y32.astype(np.float16))
+
+
+# The reference's EXL3 fixture (Tests/IshizukiKitTests/EXL3Tests.swift:23-27): rate and codebook per tensor
+EXL3_RATES = [("r1c0", 0), ("r2c1", 1), ("r3c2", 2), ("r4c0", 0), ("r5c2", 2), ("r6c1", 1), ("r7c2", 2), ("r8c0", 0),
+              ("r1h5c2", 2), ("r2h5c2", 2), ("r3h5c2", 2)]
+
+
+def test_exl3_decode_is_bit_exact_on_the_reference_fixture(golden_dir):
+    # EXL3Tests.decodeMatchesReference: every rate (1...8 bits and the half rates) and codebook
+    g = np.load(golden_dir / "exl3_reference.npz")
+    for name, codebook in EXL3_RATES:
+        got = oracle.exl3_dequantize(g[name + ".trellis"], codebook)
+        want = g[name + ".expected"]
+        assert got.shape == want.shape
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+
+
+def test_exl3_projection_reproduces_its_checkpoint(golden_dir):
+    # EXL3Tests.projectionMatchesCheckpoint: relative drift below 0.12 against the fp16 weight the
+    # projection was quantized from, both rotations included
+    g = np.load(golden_dir / "exl3_reference.npz")
+    rng = np.random.default_rng(3)
+    for name, codebook in (("qwen3", oracle.EXL3_3INST), ("qwen38", oracle.EXL3_MUL1)):
+        x = rng.standard_normal((12, 128)).astype(np.float16)
+        y = oracle.exl3_apply(x, g[name + ".trellis"], g[name + ".suh"], g[name + ".svh"], codebook).astype(np.float64)
+        want = x.astype(np.float64) @ g[name + ".weight"].astype(np.float64)
+        assert np.sqrt(((y - want) ** 2).sum() / (want ** 2).sum()) < 0.12
+
+
+def test_exl3_rotation_is_the_scaled_block_hadamard():
+    # EXL3Tests.rotationMatchesHadamard
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((7, 1024)).astype(np.float32)
+    s = rng.standard_normal(1024).astype(np.float16)
+    h = np.array([[1.0]])
+    while h.shape[0] < 128:
+        h = np.block([[h, h], [h, -h]])
+    h /= np.sqrt(128.0)
+    before = ((x * s.astype(np.float32)).reshape(-1, 128) @ h).reshape(7, 1024)
+    after = (x.reshape(-1, 128) @ h).reshape(7, 1024) * s.astype(np.float32)
+    assert np.abs(oracle.exl3_rotate(x, s, True, np.float32) - before).max() < 1e-4
+    assert np.abs(oracle.exl3_rotate(x, s, False, np.float32) - after).max() < 1e-4
