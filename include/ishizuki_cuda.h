@@ -399,6 +399,42 @@ void ishi_group_destroy(ishi_group *g);
  * with NULL. Lets the error and time-out paths be exercised on a machine without GPUs. */
 ishi_status ishi_group_debug_set_api(const void *table);
 
+/* ---- EXL3 trellis-coded projections: EXL3Tensor / EXL3Kernels ------------------------------ */
+
+enum { ISHI_EXL3_3INST = 0, ISHI_EXL3_MCG = 1, ISHI_EXL3_MUL1 = 2 };
+
+/* EXL3Tensor (Sources/IshizukiKit/Core/EXL3.swift:9-79). The weight is W [k, n] in 16 x 16 tiles
+ * of 16 * bits int16 each; bits in {1, 1.5, 2, 2.5, 3, 3.5, 4, 5, 6, 7, 8}, the half rates only with
+ * the MUL1 codebook; k and n whole numbers of 128 (EXL3.swift:28-49: ISHI_E_SHAPE /
+ * ISHI_E_UNSUPPORTED otherwise). The scale vectors are fp16 (the unpacked "suh" / "svh" form). */
+typedef struct ishi_exl3_desc {
+  const int16_t *trellis_dev;     /* [k / 16][n / 16][words_per_tile] */
+  int64_t k, n;
+  int32_t words_per_tile;         /* 16 * bits */
+  int32_t codebook;               /* ISHI_EXL3_* */
+  const void *input_scales_dev;   /* fp16 [k]; may be NULL for the kernel-level calls that do not rotate */
+  const void *output_scales_dev;  /* fp16 [n] */
+} ishi_exl3_desc;
+
+/* EXL3Kernels.dequantize (EXL3.swift:124-141, 275-292): W [k, n] as fp16 or fp32 (ISHI_DT_F16 /
+ * ISHI_DT_F32), bit-exact against the exllamav3 reconstruction in the reference's fixture. */
+ishi_status ishi_exl3_dequantize(ishi_ctx *ctx, const ishi_exl3_desc *t, int out_dtype, void *w_out, void *stream);
+/* EXL3Kernels.rotate (EXL3.swift:108-122, 219-262): block Hadamard of 128 along each row, times
+ * 1 / sqrt(128), with the fp16 scale vector applied first (before != 0) or last; fp32 inside.
+ * x and y: [rows, width], fp16 or fp32 each. */
+ishi_status ishi_exl3_rotate(ishi_ctx *ctx, const void *x, int x_dtype, int64_t rows, int64_t width,
+                             const void *scales_dev, int before, void *y, int y_dtype, void *stream);
+/* EXL3Kernels.matvec (EXL3.swift:143-163, 294-343): y [rows, n] fp32 = x [rows, k] fp16 . W for
+ * 1...8 rows, the tiles decoded straight into tensor-core operands (a tile's weight order is the
+ * A fragment of mma.sync m16n8k16 with n on the M side); no rotation. */
+ishi_status ishi_exl3_matvec(ishi_ctx *ctx, const ishi_exl3_desc *t, const void *x, int rows, float *y, void *stream);
+/* EXL3Kernels.apply (EXL3.swift:83-106): rotate x with the input scales (to fp16), multiply, rotate
+ * the fp32 product with the output scales; y [rows, n] fp16, 1...16 rows (9...16 as two products,
+ * as the reference does; its dense route above 16 rows is not part of this library: ISHI_E_SHAPE).
+ * Uses scratch of the context, grown on demand by the first call of a larger shape (which then
+ * allocates and must not be captured into a graph). */
+ishi_status ishi_exl3_apply(ishi_ctx *ctx, const ishi_exl3_desc *t, const void *x, int rows, void *y, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

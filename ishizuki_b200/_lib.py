@@ -15,6 +15,7 @@ GGML_TYPE_SIZE = {10: 84, 12: 144, 14: 210, 16: 66, 17: 74, 18: 98, 19: 50, 21: 
 KIND_AFFINE, KIND_GGML = 0, 1
 DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 ROUTE_AUTO, ROUTE_GEMV, ROUTE_MMA = 0, 1, 2
+EXL3_3INST, EXL3_MCG, EXL3_MUL1 = 0, 1, 2
 OUT_TRANSPOSED = 1
 EXCHANGE_HANDLE_BYTES = 128
 
@@ -34,6 +35,14 @@ class WeightDesc(ctypes.Structure):
     ]
 
 
+class EXL3Desc(ctypes.Structure):
+    _fields_ = [
+        ("trellis_dev", c_void_p), ("k", c_int64), ("n", c_int64),
+        ("words_per_tile", c_int32), ("codebook", c_int32),
+        ("input_scales_dev", c_void_p), ("output_scales_dev", c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "ishi_ctx_create": (c_int, [c_int, POINTER(c_void_p)]),
@@ -45,6 +54,10 @@ SIGNATURES = {
     "ishi_projection_create": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(c_void_p)]),
     "ishi_projection_create_fused": (c_int, [c_void_p, POINTER(WeightDesc), c_int, POINTER(c_void_p)]),
     "ishi_projection_create_gated": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(WeightDesc), POINTER(c_void_p)]),
+    "ishi_exl3_dequantize": (c_int, [c_void_p, POINTER(EXL3Desc), c_int, c_void_p, c_void_p]),
+    "ishi_exl3_rotate": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "ishi_exl3_matvec": (c_int, [c_void_p, POINTER(EXL3Desc), c_void_p, c_int, c_void_p, c_void_p]),
+    "ishi_exl3_apply": (c_int, [c_void_p, POINTER(EXL3Desc), c_void_p, c_int, c_void_p, c_void_p]),
     "ishi_projection_destroy": (None, [c_void_p]),
     "ishi_projection_input_dim": (c_int64, [c_void_p]),
     "ishi_projection_output_dim": (c_int64, [c_void_p]),

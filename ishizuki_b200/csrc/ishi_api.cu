@@ -81,6 +81,9 @@ struct ishi_ctx {
   void *pin_x = nullptr, *pin_y = nullptr;  // pinned staging for apply_host
   void *dev_x = nullptr, *dev_y = nullptr;
   size_t pin_x_bytes = 0, pin_y_bytes = 0;
+  __half *exl3_x = nullptr;  // ishi_exl3_apply: rotated activations [16][k] and fp32 products [16][n]
+  float *exl3_y = nullptr;
+  size_t exl3_x_cap = 0, exl3_y_cap = 0;
   // apply_host_batch: its two copy streams and the events that order them against the caller's stream
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   std::vector<cudaEvent_t> ev_in, ev_done;
@@ -769,6 +772,8 @@ void ishi_ctx_destroy(ishi_ctx *ctx) {
   if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
   if (ctx->dev_x) cudaFree(ctx->dev_x);
   if (ctx->dev_y) cudaFree(ctx->dev_y);
+  if (ctx->exl3_x) cudaFree(ctx->exl3_x);
+  if (ctx->exl3_y) cudaFree(ctx->exl3_y);
   for (cudaEvent_t e : ctx->ev_in) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->ev_done) cudaEventDestroy(e);
   if (ctx->ev_begin) cudaEventDestroy(ctx->ev_begin);
@@ -1598,4 +1603,92 @@ extern "C" ishi_status ishi_q4k_matmul_few_static(const void *x, int rows, const
   int raised = 0;
   if (cudaMemcpy(&raised, b + kStaticErr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return ISHI_E_CUDA;
   return raised ? ISHI_E_TIMEOUT : ISHI_OK;
+}
+
+// ---- EXL3 -----------------------------------------------------------------------------------------
+
+namespace {
+// EXL3Tensor.init's guards (Sources/IshizukiKit/Core/EXL3.swift:28-49)
+ishi_status check_exl3(ishi_ctx *ctx, const ishi_exl3_desc *t, bool need_scales) {
+  if (!t || !t->trellis_dev) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(t->trellis_dev) & 3u) return fail(ctx, ISHI_E_INVALID, "trellis not 4-byte aligned");
+  if (!exl3_rate_supported(t->words_per_tile, t->codebook))
+    return fail(ctx, ISHI_E_UNSUPPORTED, "an EXL3 tile of %d words with codebook %d is not a rate", t->words_per_tile, t->codebook);
+  if (t->k <= 0 || t->n <= 0 || t->k % 128 != 0 || t->n % 128 != 0 || t->k > (1ll << 24) || t->n > (1ll << 24))
+    return fail(ctx, ISHI_E_SHAPE, "EXL3 %lldx%lld is not a whole number of 128 blocks", (long long)t->k, (long long)t->n);
+  if (need_scales && (!t->input_scales_dev || !t->output_scales_dev)) return fail(ctx, ISHI_E_INVALID, "null scale vector");
+  return ISHI_OK;
+}
+}  // namespace
+
+ishi_status ishi_exl3_dequantize(ishi_ctx *ctx, const ishi_exl3_desc *t, int out_dtype, void *w_out, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  ishi_status s = check_exl3(ctx, t, false);
+  if (s != ISHI_OK) return s;
+  if (!w_out) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (out_dtype != ISHI_DT_F16 && out_dtype != ISHI_DT_F32) return fail(ctx, ISHI_E_INVALID, "bad output dtype %d", out_dtype);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ISHI_CUDA(ctx, launch_exl3_dequantize(t->trellis_dev, (int)(t->k / 16), (int)(t->n / 16), t->words_per_tile, t->codebook, w_out,
+                                        out_dtype, ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  return ISHI_OK;
+}
+
+ishi_status ishi_exl3_rotate(ishi_ctx *ctx, const void *x, int x_dtype, int64_t rows, int64_t width, const void *scales_dev,
+                             int before, void *y, int y_dtype, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  if (!x || !y || !scales_dev) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if ((x_dtype != ISHI_DT_F16 && x_dtype != ISHI_DT_F32) || (y_dtype != ISHI_DT_F16 && y_dtype != ISHI_DT_F32))
+    return fail(ctx, ISHI_E_INVALID, "bad dtype");
+  if (rows < 0 || width <= 0 || width % 128 != 0) return fail(ctx, ISHI_E_SHAPE, "width %lld is not a whole number of 128 blocks", (long long)width);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ISHI_CUDA(ctx, launch_exl3_rotate(x, x_dtype, rows, width, static_cast<const __half *>(scales_dev), before ? 1 : 0, y, y_dtype,
+                                    ctx->sm_count, static_cast<cudaStream_t>(stream)));
+  return ISHI_OK;
+}
+
+ishi_status ishi_exl3_matvec(ishi_ctx *ctx, const ishi_exl3_desc *t, const void *x, int rows, float *y, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  ishi_status s = check_exl3(ctx, t, false);
+  if (s != ISHI_OK) return s;
+  if (!x || !y) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(x) & 3u) return fail(ctx, ISHI_E_INVALID, "x must be 4-byte aligned");
+  if (rows < 1 || rows > 8) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...8", rows);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ISHI_CUDA(ctx, launch_exl3_matvec(t->trellis_dev, (int)(t->k / 16), (int)(t->n / 16), t->words_per_tile, t->codebook,
+                                    static_cast<const __half *>(x), rows, y, static_cast<cudaStream_t>(stream)));
+  return ISHI_OK;
+}
+
+ishi_status ishi_exl3_apply(ishi_ctx *ctx, const ishi_exl3_desc *t, const void *x, int rows, void *y, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  ishi_status s = check_exl3(ctx, t, true);
+  if (s != ISHI_OK) return s;
+  if (!x || !y) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if (rows < 1 || rows > 16) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...16", rows);
+  std::lock_guard<std::mutex> g(ctx->lock);
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t xb = (size_t)16 * t->k * sizeof(__half), yb = (size_t)16 * t->n * sizeof(float);
+  if (ctx->exl3_x_cap < xb) {
+    ISHI_CUDA(ctx, cudaStreamSynchronize(st));  // earlier calls may still read the smaller buffer
+    if (ctx->exl3_x) cudaFree(ctx->exl3_x);
+    ctx->exl3_x = nullptr, ctx->exl3_x_cap = 0;
+    ISHI_CUDA(ctx, cudaMalloc(&ctx->exl3_x, xb));
+    ctx->exl3_x_cap = xb;
+  }
+  if (ctx->exl3_y_cap < yb) {
+    ISHI_CUDA(ctx, cudaStreamSynchronize(st));
+    if (ctx->exl3_y) cudaFree(ctx->exl3_y);
+    ctx->exl3_y = nullptr, ctx->exl3_y_cap = 0;
+    ISHI_CUDA(ctx, cudaMalloc(&ctx->exl3_y, yb));
+    ctx->exl3_y_cap = yb;
+  }
+  ISHI_CUDA(ctx, launch_exl3_rotate(x, ISHI_DT_F16, rows, t->k, static_cast<const __half *>(t->input_scales_dev), 1, ctx->exl3_x,
+                                    ISHI_DT_F16, ctx->sm_count, st));
+  for (int r0 = 0; r0 < rows; r0 += 8)
+    ISHI_CUDA(ctx, launch_exl3_matvec(t->trellis_dev, (int)(t->k / 16), (int)(t->n / 16), t->words_per_tile, t->codebook,
+                                      ctx->exl3_x + (size_t)r0 * t->k, std::min(8, rows - r0), ctx->exl3_y + (size_t)r0 * t->n, st));
+  ISHI_CUDA(ctx, launch_exl3_rotate(ctx->exl3_y, ISHI_DT_F32, rows, t->n, static_cast<const __half *>(t->output_scales_dev), 0, y,
+                                    ISHI_DT_F16, ctx->sm_count, st));
+  return ISHI_OK;
 }

@@ -47,4 +47,14 @@ cudaError_t launch_ggml_rowdot(int type, const uint8_t *blocks, long long n, lon
                                long long ldy, int transposed, int sm_count, cudaStream_t st);
 cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, cudaStream_t st);
 
+// ---- EXL3 trellis-coded weights (ishi_exl3.cu) ---------------------------------------------------
+// words16: int16 words per 16 x 16 tile (16 * bits); codebook: 0 3INST, 1 MCG, 2 MUL1; dtypes: 0 fp16, 2 fp32
+bool exl3_rate_supported(int words16, int codebook);
+cudaError_t launch_exl3_dequantize(const int16_t *trellis, int tiles_k, int tiles_n, int words16, int codebook, void *out,
+                                   int out_dtype, int sm_count, cudaStream_t st);
+cudaError_t launch_exl3_matvec(const int16_t *trellis, int tiles_k, int tiles_n, int words16, int codebook, const __half *x,
+                               int rows, float *y, cudaStream_t st);
+cudaError_t launch_exl3_rotate(const void *x, int x_dtype, long long rows, long long width, const __half *scales, int before,
+                               void *y, int y_dtype, int sm_count, cudaStream_t st);
+
 }  // namespace ishi

@@ -502,3 +502,77 @@ def hadamardRotate(x: torch.Tensor, block: int, signs: torch.Tensor | None) -> t
     if rc != _lib.OK:
         raise IshizukiError(rc, ctx.last_error())
     return y.reshape(x.shape)
+
+
+class EXL3Tensor:
+    """An EXL3 trellis-coded weight (reference: EXL3Tensor, Sources/IshizukiKit/Core/EXL3.swift:9-79):
+    ``trellis`` int16 [k / 16, n / 16, 16 * bits], fp16 scale vectors of the input and the output
+    side, and one of the three codebooks."""
+
+    threeInst, mcg, mul1 = _lib.EXL3_3INST, _lib.EXL3_MCG, _lib.EXL3_MUL1
+
+    def __init__(self, trellis: torch.Tensor, inputScales: torch.Tensor | None, outputScales: torch.Tensor | None,  # noqa: N803
+                 codebook: int):
+        if trellis.ndim != 3 or trellis.dtype != torch.int16:
+            raise ValueError("EXL3 trellis must be int16 [k/16, n/16, words]")
+        self.trellis = trellis.contiguous()
+        self.inputScales = None if inputScales is None else inputScales.to(torch.float16).reshape(-1).contiguous()
+        self.outputScales = None if outputScales is None else outputScales.to(torch.float16).reshape(-1).contiguous()
+        self.codebook = int(codebook)
+        self.bits = trellis.shape[2] / 16
+        self.inputDim, self.outputDim = trellis.shape[0] * 16, trellis.shape[1] * 16
+
+    def _desc(self) -> "_lib.EXL3Desc":
+        d = _lib.EXL3Desc()
+        d.trellis_dev = self.trellis.data_ptr()
+        d.k, d.n = self.inputDim, self.outputDim
+        d.words_per_tile = self.trellis.shape[2]
+        d.codebook = self.codebook
+        d.input_scales_dev = 0 if self.inputScales is None else self.inputScales.data_ptr()
+        d.output_scales_dev = 0 if self.outputScales is None else self.outputScales.data_ptr()
+        return d
+
+
+class EXL3Kernels:
+    """EXL3Kernels of the reference (EXL3.swift:81-164): decode, rotations, the few-row product
+    that decodes inside the multiply, and their composition."""
+
+    matvecRows = range(1, 9)
+
+    @staticmethod
+    def dequantize(t: EXL3Tensor, dtype: torch.dtype = torch.float16) -> torch.Tensor:
+        ctx = Context.get(t.trellis.device.index)
+        w = torch.empty((t.inputDim, t.outputDim), dtype=dtype, device=t.trellis.device)
+        ctx.check(ctx.lib.ishi_exl3_dequantize(ctx.handle, ctypes.byref(t._desc()), _OUT_DT[dtype], _ptr(w), _stream()), declined=())
+        return w
+
+    @staticmethod
+    def rotate(x: torch.Tensor, scales: torch.Tensor, before: bool, to: torch.dtype) -> torch.Tensor:
+        ctx = Context.get(x.device.index)
+        h = x.reshape(-1, x.shape[-1]).contiguous()
+        s = scales.to(torch.float16).contiguous()
+        y = torch.empty(h.shape, dtype=to, device=x.device)
+        ctx.check(ctx.lib.ishi_exl3_rotate(ctx.handle, _ptr(h), _OUT_DT[h.dtype], h.shape[0], h.shape[1], _ptr(s), int(before),
+                                           _ptr(y), _OUT_DT[to], _stream()), declined=())
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def matvec(x: torch.Tensor, t: EXL3Tensor) -> torch.Tensor | None:
+        """fp32 [rows, n] for 1...8 fp16 rows, None outside (as the reference)."""
+        if x.ndim != 2 or x.shape[1] != t.inputDim or x.shape[0] not in EXL3Kernels.matvecRows:
+            return None
+        ctx = Context.get(x.device.index)
+        h = x.to(torch.float16).contiguous()
+        y = torch.empty((h.shape[0], t.outputDim), dtype=torch.float32, device=x.device)
+        ctx.check(ctx.lib.ishi_exl3_matvec(ctx.handle, ctypes.byref(t._desc()), _ptr(h), h.shape[0], _ptr(y), _stream()), declined=())
+        return y
+
+    @staticmethod
+    def apply(x: torch.Tensor, t: EXL3Tensor) -> torch.Tensor:
+        """rotate -> product -> rotate, 1...16 fp16 rows."""
+        ctx = Context.get(x.device.index)
+        shape = x.shape
+        h = x.reshape(-1, t.inputDim).to(torch.float16).contiguous()
+        y = torch.empty((h.shape[0], t.outputDim), dtype=torch.float16, device=x.device)
+        ctx.check(ctx.lib.ishi_exl3_apply(ctx.handle, ctypes.byref(t._desc()), _ptr(h), h.shape[0], _ptr(y), _stream()), declined=())
+        return y.reshape(shape[:-1] + (t.outputDim,))
