@@ -474,6 +474,26 @@ def format_table(peak: float) -> dict:
     table["q4_k_mlp_block_m8"] = row
     del mlps
     torch.cuda.empty_cache()
+    # EXL3 trellis-coded weights on the gate shape, 4 bits, the product kernel alone (no rotations)
+    from ishizuki_b200.interface import EXL3Kernels, EXL3Tensor
+
+    for name, codebook in (("exl3_4bit_3inst", EXL3Tensor.threeInst), ("exl3_4bit_mul1", EXL3Tensor.mul1)):
+        tensors = [EXL3Tensor(torch.randint(-32768, 32768, (k // 16, n // 16, 64), dtype=torch.int16, device="cuda"), None, None,
+                              codebook) for _ in range(copies)]
+        row = {"weight_mb": tensors[0].trellis.numel() * 2 / 1e6}
+        for m in (1, 8):
+            x = dev(synth.activations(rng, m, k))
+
+            def run():
+                for t in tensors:
+                    EXL3Kernels.matvec(x, t)
+
+            us = timed_graph(run) / copies
+            gbs = row["weight_mb"] * 1e3 / us
+            row["m%d" % m] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+        table[name] = row
+        del tensors
+    torch.cuda.empty_cache()
     return table
 
 

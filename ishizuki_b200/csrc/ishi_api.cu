@@ -1655,7 +1655,7 @@ ishi_status ishi_exl3_matvec(ishi_ctx *ctx, const ishi_exl3_desc *t, const void 
   if (rows < 1 || rows > 8) return fail(ctx, ISHI_E_SHAPE, "rows %d outside 1...8", rows);
   ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
   ISHI_CUDA(ctx, launch_exl3_matvec(t->trellis_dev, (int)(t->k / 16), (int)(t->n / 16), t->words_per_tile, t->codebook,
-                                    static_cast<const __half *>(x), rows, y, static_cast<cudaStream_t>(stream)));
+                                    static_cast<const __half *>(x), rows, y, ctx->sm_count, static_cast<cudaStream_t>(stream)));
   return ISHI_OK;
 }
 
@@ -1687,7 +1687,7 @@ ishi_status ishi_exl3_apply(ishi_ctx *ctx, const ishi_exl3_desc *t, const void *
                                     ISHI_DT_F16, ctx->sm_count, st));
   for (int r0 = 0; r0 < rows; r0 += 8)
     ISHI_CUDA(ctx, launch_exl3_matvec(t->trellis_dev, (int)(t->k / 16), (int)(t->n / 16), t->words_per_tile, t->codebook,
-                                      ctx->exl3_x + (size_t)r0 * t->k, std::min(8, rows - r0), ctx->exl3_y + (size_t)r0 * t->n, st));
+                                      ctx->exl3_x + (size_t)r0 * t->k, std::min(8, rows - r0), ctx->exl3_y + (size_t)r0 * t->n, ctx->sm_count, st));
   ISHI_CUDA(ctx, launch_exl3_rotate(ctx->exl3_y, ISHI_DT_F32, rows, t->n, static_cast<const __half *>(t->output_scales_dev), 0, y,
                                     ISHI_DT_F16, ctx->sm_count, st));
   return ISHI_OK;

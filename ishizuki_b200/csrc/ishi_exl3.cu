@@ -45,9 +45,10 @@ __host__ __device__ constexpr uint32_t exl3_rel(uint32_t i) {
 template <bool MUL1>
 __device__ __forceinline__ uint32_t exl3_pair(uint32_t s0, uint32_t s1, uint32_t mult, uint32_t add) {
   if (MUL1) {
-    const uint32_t x0 = s0 * 0x83DCD12Du, x1 = s1 * 0x83DCD12Du;
-    const uint32_t p0 = (x0 & 0x00ff00ffu) + ((x0 >> 8) & 0x00ff00ffu), p1 = (x1 & 0x00ff00ffu) + ((x1 >> 8) & 0x00ff00ffu);
-    const uint32_t h = (((p0 & 0xffffu) + (p0 >> 16)) | (((p1 & 0xffffu) + (p1 >> 16)) << 16)) + 0x64006400u;
+    // the byte sums through the four-way byte dot product with 0x6400 as its addend; the second
+    // weight's sum, moved to the upper half, is the addend of the first
+    const uint32_t m1 = __dp4a(s1 * 0x83DCD12Du, 0x01010101u, 0x6400u);
+    const uint32_t h = __dp4a(s0 * 0x83DCD12Du, 0x01010101u, (m1 << 16) + 0x6400u);
     const uint32_t m = 0x1eee1eeeu, b = 0xc931c931u;
     const __half2 r = __hfma2(*reinterpret_cast<const __half2 *>(&h), *reinterpret_cast<const __half2 *>(&m),
                               *reinterpret_cast<const __half2 *>(&b));
@@ -60,17 +61,26 @@ __device__ __forceinline__ uint32_t exl3_pair(uint32_t s0, uint32_t s1, uint32_t
   return *reinterpret_cast<const uint32_t *>(&r);
 }
 
-// lane's eight weights of one tile as four fp16 pairs (v0 v1 | v2 v3 | v4 v5 | v6 v7)
+// Which three consecutive ring words (with wrap-around) hold lane's eight 16-bit windows, and the
+// bit of the first word where the first window starts. The same for every tile of a rate.
+template <int KA, bool HK>
+struct Exl3Lane {
+  uint32_t j0, j1, j2, sh;
+  __device__ __forceinline__ explicit Exl3Lane(int lane) {
+    constexpr uint32_t kRing = exl3_ring(KA, HK), kWords = kRing / 32;
+    const uint32_t lo = exl3_end<KA, HK>((uint32_t)lane * 8u) + kRing - 16u;  // first bit of the first window
+    const uint32_t i0 = lo >> 5;
+    sh = lo & 31u;
+    j0 = i0 >= kWords ? i0 - kWords : i0;
+    j1 = j0 + 1 >= kWords ? j0 + 1 - kWords : j0 + 1;
+    j2 = j1 + 1 >= kWords ? j1 + 1 - kWords : j1 + 1;
+  }
+};
+
+// lane's eight weights of one tile, from its three ring words, as four fp16 pairs (v0 v1 | v2 v3 | v4 v5 | v6 v7)
 template <int KA, bool HK, bool MUL1>
-__device__ __forceinline__ void exl3_decode8(const uint32_t *__restrict__ tile, int lane, uint32_t mult, uint32_t add,
+__device__ __forceinline__ void exl3_decode8(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t sh, uint32_t mult, uint32_t add,
                                              uint32_t (&v)[4]) {
-  constexpr uint32_t kRing = exl3_ring(KA, HK), kWords = kRing / 32;
-  const uint32_t lo = exl3_end<KA, HK>((uint32_t)lane * 8u) + kRing - 16u;  // first bit of the first window
-  const uint32_t i0 = lo >> 5, sh = lo & 31u;
-  const uint32_t j0 = i0 >= kWords ? i0 - kWords : i0;
-  const uint32_t j1 = j0 + 1 >= kWords ? j0 + 1 - kWords : j0 + 1;
-  const uint32_t j2 = j1 + 1 >= kWords ? j1 + 1 - kWords : j1 + 1;
-  const uint32_t w0 = __ldg(tile + j0), w1 = __ldg(tile + j1), w2 = __ldg(tile + j2);
   // 96 ring bits from the window's first bit on: b0 (top) b1 b2
   const uint32_t b0 = __funnelshift_l(w1, w0, sh), b1 = __funnelshift_l(w2, w1, sh), b2 = w2 << sh;
   uint32_t s[8];
@@ -98,7 +108,9 @@ __global__ void __launch_bounds__(256) exl3_dequantize_kernel(const uint32_t *__
   const long long N = (long long)tiles_n * 16;
   for (long long tile = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); tile < total; tile += (long long)gridDim.x * 8) {
     uint32_t v[4];
-    exl3_decode8<KA, HK, MUL1>(trellis + tile * kWords, lane, mult, add, v);
+    const Exl3Lane<KA, HK> at(lane);
+    const uint32_t *words = trellis + tile * kWords;
+    exl3_decode8<KA, HK, MUL1>(__ldg(words + at.j0), __ldg(words + at.j1), __ldg(words + at.j2), at.sh, mult, add, v);
     const long long row = (tile / tiles_n) * 16 + (lane & 3) * 2, col = (tile % tiles_n) * 16 + (lane >> 2);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -111,51 +123,73 @@ __global__ void __launch_bounds__(256) exl3_dequantize_kernel(const uint32_t *__
 }
 
 // ---- the product: y [rows][n] fp32 = x [rows][k] fp16 . W --------------------------------------------
-// One CTA per tile column (16 outputs), its eight warps split the k tiles; a warp decodes a tile
-// into its A fragment and multiplies it with the matching 16 inputs of up to eight rows (B: lane
-// (g, t) reads x[g][16 tk + 2t, 2t + 1] and [.. + 8, + 9]). Tiles of a column are n / 16 tiles apart in
-// memory: each is one or a few full cache lines. The warps' partial 16 x 8 tiles are added through
-// shared memory in a fixed order.
-template <int KA, bool HK, bool MUL1>
-__global__ void __launch_bounds__(256) exl3_matvec_kernel(const uint32_t *__restrict__ trellis, int tiles_k, int tiles_n,
-                                                          uint32_t mult, uint32_t add, const __half *__restrict__ x, int rows,
-                                                          long long K, float *__restrict__ y) {
+// One CTA per C adjacent tile columns (16 C outputs), its sixteen warps split the k tiles. For a k
+// tile a warp reads the matching 16 inputs of up to eight rows once (B: lane (g, t) reads
+// x[g][16 tk + 2t, 2t + 1] and [.. + 8, + 9]), decodes the C tiles, which lie one after the other in
+// memory, each into its A fragment, and multiplies. The words of two k tiles are requested before
+// the first is decoded. The warps' partial 16 x 8 tiles are added through shared memory in a
+// fixed order.
+constexpr int kExl3Warps = 16;
+template <int KA, bool HK, bool MUL1, int C>
+__global__ void __launch_bounds__(kExl3Warps * 32) exl3_matvec_kernel(const uint32_t *__restrict__ trellis, int tiles_k, int tiles_n,
+                                                                      uint32_t mult, uint32_t add, const __half *__restrict__ x,
+                                                                      int rows, long long K, float *__restrict__ y) {
   constexpr uint32_t kWords = exl3_ring(KA, HK) / 32;
-  __shared__ float red[8][32][4];
+  __shared__ float red[kExl3Warps][C][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int tn = blockIdx.x;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint32_t *column = trellis + (long long)tn * kWords;
+  const int tn0 = blockIdx.x * C;
+  float acc[C][4];
+#pragma unroll
+  for (int c = 0; c < C; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+  const Exl3Lane<KA, HK> at(lane);
+  const uint32_t *column = trellis + (long long)tn0 * kWords;
   const long long tile_stride = (long long)tiles_n * kWords;
   const uint32_t *xr = reinterpret_cast<const uint32_t *>(x + (long long)g * K) + t;  // pairs of inputs
   const bool live = g < rows;
-  constexpr int kUnroll = 4;
-  for (int tk0 = warp; tk0 < tiles_k; tk0 += 8 * kUnroll) {
-    uint32_t v[kUnroll][4], b[kUnroll][2];
+  constexpr int kUnroll = 2;
+  for (int tk0 = warp; tk0 < tiles_k; tk0 += kExl3Warps * kUnroll) {
+    uint32_t w[kUnroll][C][3], b[kUnroll][2];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int tk = tk0 + 8 * u;
+      const int tk = tk0 + kExl3Warps * u;
       if (tk < tiles_k) {
-        exl3_decode8<KA, HK, MUL1>(column + tk * tile_stride, lane, mult, add, v[u]);
+        const uint32_t *tiles = column + tk * tile_stride;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          w[u][c][0] = __ldg(tiles + c * kWords + at.j0);
+          w[u][c][1] = __ldg(tiles + c * kWords + at.j1);
+          w[u][c][2] = __ldg(tiles + c * kWords + at.j2);
+        }
         b[u][0] = live ? __ldg(xr + tk * 8) : 0u;
         b[u][1] = live ? __ldg(xr + tk * 8 + 4) : 0u;
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
-      if (tk0 + 8 * u < tiles_k) mma16816(acc, v[u][0], v[u][2], v[u][1], v[u][3], b[u][0], b[u][1]);
+    for (int u = 0; u < kUnroll; ++u) {
+      if (tk0 + kExl3Warps * u < tiles_k) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          uint32_t v[4];
+          exl3_decode8<KA, HK, MUL1>(w[u][c][0], w[u][c][1], w[u][c][2], at.sh, mult, add, v);
+          mma16816(acc[c], v[0], v[2], v[1], v[3], b[u][0], b[u][1]);
+        }
+      }
+    }
   }
-  red[warp][lane][0] = acc[0], red[warp][lane][1] = acc[1], red[warp][lane][2] = acc[2], red[warp][lane][3] = acc[3];
+#pragma unroll
+  for (int c = 0; c < C; ++c)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp][c][lane][i] = acc[c][i];
   __syncthreads();
-  if (threadIdx.x < 128) {
-    const int l = threadIdx.x >> 2, i = threadIdx.x & 3;  // accumulator i of lane l
+  for (int e = threadIdx.x; e < C * 128; e += kExl3Warps * 32) {
+    const int c = e >> 7, l = (e >> 2) & 31, i = e & 3;  // accumulator i of lane l, column c
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) s += red[w][l][i];
+    for (int w = 0; w < kExl3Warps; ++w) s += red[w][c][l][i];
     // lane (g, t): c0, c1 = output g, rows 2t, 2t + 1; c2, c3 = output g + 8
     const int out = (l >> 2) + ((i & 2) ? 8 : 0), m = 2 * (l & 3) + (i & 1);
-    if (m < rows) y[(long long)m * tiles_n * 16 + tn * 16 + out] = s;
+    if (m < rows) y[(long long)m * tiles_n * 16 + (tn0 + c) * 16 + out] = s;
   }
 }
 
@@ -205,10 +239,18 @@ cudaError_t dequantize_as(const uint32_t *trellis, int tiles_k, int tiles_n, uin
   return cudaGetLastError();
 }
 
+// C tile columns per CTA: as many (up to four) as still leave one and a half CTAs per SM
 template <int KA, bool HK, bool MUL1>
 cudaError_t matvec_as(const uint32_t *trellis, int tiles_k, int tiles_n, uint32_t mult, uint32_t add, const __half *x, int rows,
-                      float *y, cudaStream_t st) {
-  exl3_matvec_kernel<KA, HK, MUL1><<<tiles_n, 256, 0, st>>>(trellis, tiles_k, tiles_n, mult, add, x, rows, (long long)tiles_k * 16, y);
+                      float *y, int sm_count, cudaStream_t st) {
+  const long long K = (long long)tiles_k * 16;
+  const int threads = kExl3Warps * 32;
+  if (tiles_n % 4 == 0 && tiles_n / 4 >= sm_count * 3 / 2)
+    exl3_matvec_kernel<KA, HK, MUL1, 4><<<tiles_n / 4, threads, 0, st>>>(trellis, tiles_k, tiles_n, mult, add, x, rows, K, y);
+  else if (tiles_n % 2 == 0 && tiles_n / 2 >= sm_count * 3 / 2)
+    exl3_matvec_kernel<KA, HK, MUL1, 2><<<tiles_n / 2, threads, 0, st>>>(trellis, tiles_k, tiles_n, mult, add, x, rows, K, y);
+  else
+    exl3_matvec_kernel<KA, HK, MUL1, 1><<<tiles_n, threads, 0, st>>>(trellis, tiles_k, tiles_n, mult, add, x, rows, K, y);
   return cudaGetLastError();
 }
 
@@ -269,12 +311,12 @@ cudaError_t launch_exl3_dequantize(const int16_t *trellis, int tiles_k, int tile
 }
 
 cudaError_t launch_exl3_matvec(const int16_t *trellis, int tiles_k, int tiles_n, int words16, int codebook, const __half *x,
-                               int rows, float *y, cudaStream_t st) {
+                               int rows, float *y, int sm_count, cudaStream_t st) {
   uint32_t mult, add;
   codebook_constants(codebook, &mult, &add);
   return by_rate(words16, codebook, [&](auto ka, auto hk, auto mul1) {
     return matvec_as<decltype(ka)::value, decltype(hk)::value, decltype(mul1)::value>(reinterpret_cast<const uint32_t *>(trellis),
-                                                                                      tiles_k, tiles_n, mult, add, x, rows, y, st);
+                                                                                      tiles_k, tiles_n, mult, add, x, rows, y, sm_count, st);
   });
 }
 

@@ -53,7 +53,7 @@ bool exl3_rate_supported(int words16, int codebook);
 cudaError_t launch_exl3_dequantize(const int16_t *trellis, int tiles_k, int tiles_n, int words16, int codebook, void *out,
                                    int out_dtype, int sm_count, cudaStream_t st);
 cudaError_t launch_exl3_matvec(const int16_t *trellis, int tiles_k, int tiles_n, int words16, int codebook, const __half *x,
-                               int rows, float *y, cudaStream_t st);
+                               int rows, float *y, int sm_count, cudaStream_t st);
 cudaError_t launch_exl3_rotate(const void *x, int x_dtype, long long rows, long long width, const __half *scales, int before,
                                void *y, int y_dtype, int sm_count, cudaStream_t st);
 

@@ -576,3 +576,22 @@ class EXL3Kernels:
         y = torch.empty((h.shape[0], t.outputDim), dtype=torch.float16, device=x.device)
         ctx.check(ctx.lib.ishi_exl3_apply(ctx.handle, ctypes.byref(t._desc()), _ptr(h), h.shape[0], _ptr(y), _stream()), declined=())
         return y.reshape(shape[:-1] + (t.outputDim,))
+
+
+class EXL3Linear:
+    """PackedLinear(exl3:) of the reference (EXL3Tests.projectionMatchesCheckpoint): a projection
+    over an EXL3Tensor, y = EXL3Kernels.apply(x, tensor)."""
+
+    def __init__(self, exl3: EXL3Tensor):
+        if exl3.inputScales is None or exl3.outputScales is None:
+            raise ValueError("an EXL3 projection needs both scale vectors")
+        self.exl3 = exl3
+        self.inputDim, self.outputDim = exl3.inputDim, exl3.outputDim
+        self.ctx = Context.get(exl3.trellis.device.index)
+
+    @property
+    def weightBytes(self) -> int:  # noqa: N802
+        return self.exl3.trellis.numel() * 2 + (self.inputDim + self.outputDim) * 2
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return EXL3Kernels.apply(x, self.exl3)
