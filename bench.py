@@ -363,6 +363,29 @@ def format_table(peak: float) -> dict:
     # ISHI_BENCH_FORMATS=name[,name]: only these rows of the first group (profiler captures of one format)
     only = [f for f in os.environ.get("ISHI_BENCH_FORMATS", "").split(",") if f]
     row_counts = [int(r) for r in os.environ.get("ISHI_BENCH_ROWS", "1,8").split(",")]  # activation rows M
+    def exl3_rows():
+        # EXL3 trellis-coded weights on the gate shape, 4 bits, the product kernel alone (no rotations)
+        from ishizuki_b200.interface import EXL3Kernels, EXL3Tensor
+
+        for name, codebook in (("exl3_4bit_3inst", EXL3Tensor.threeInst), ("exl3_4bit_mul1", EXL3Tensor.mul1)):
+            if only and name not in only:
+                continue
+            tensors = [EXL3Tensor(torch.randint(-32768, 32768, (k // 16, n // 16, 64), dtype=torch.int16, device="cuda"), None,
+                                  None, codebook) for _ in range(copies)]
+            row = {"weight_mb": tensors[0].trellis.numel() * 2 / 1e6}
+            for m in row_counts:
+                x = dev(synth.activations(rng, m, k))
+
+                def run():
+                    for t in tensors:
+                        EXL3Kernels.matvec(x, t)
+
+                us = timed_graph(run) / copies
+                gbs = row["weight_mb"] * 1e3 / us
+                row["m%d" % m] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+            table[name] = row
+            del tensors
+
     for fmt in ("q4_k", "affine4_g64", "ternary2_g128_h128", "iq2_xs", "q6_k"):
         if only and fmt not in only:
             continue
@@ -390,6 +413,7 @@ def format_table(peak: float) -> dict:
         del lins
         torch.cuda.empty_cache()
     if only:
+        exl3_rows()
         return table
     # one row on CUDA cores beside the tensor-core kernel on the smallest and the tallest projection
     for name, n_, k_ in (("q4_k_kv_1024x5120", 1024, 5120), ("q4_k_down_5120x17408", 5120, 17408)):
@@ -474,25 +498,7 @@ def format_table(peak: float) -> dict:
     table["q4_k_mlp_block_m8"] = row
     del mlps
     torch.cuda.empty_cache()
-    # EXL3 trellis-coded weights on the gate shape, 4 bits, the product kernel alone (no rotations)
-    from ishizuki_b200.interface import EXL3Kernels, EXL3Tensor
-
-    for name, codebook in (("exl3_4bit_3inst", EXL3Tensor.threeInst), ("exl3_4bit_mul1", EXL3Tensor.mul1)):
-        tensors = [EXL3Tensor(torch.randint(-32768, 32768, (k // 16, n // 16, 64), dtype=torch.int16, device="cuda"), None, None,
-                              codebook) for _ in range(copies)]
-        row = {"weight_mb": tensors[0].trellis.numel() * 2 / 1e6}
-        for m in (1, 8):
-            x = dev(synth.activations(rng, m, k))
-
-            def run():
-                for t in tensors:
-                    EXL3Kernels.matvec(x, t)
-
-            us = timed_graph(run) / copies
-            gbs = row["weight_mb"] * 1e3 / us
-            row["m%d" % m] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
-        table[name] = row
-        del tensors
+    exl3_rows()
     torch.cuda.empty_cache()
     return table
 
