@@ -490,9 +490,29 @@ def format_table(peak: float) -> dict:
             torch.mul(torch.nn.functional.silu(gu[:, :17408]), gu[:, 17408:], out=h)
             down(h, out=y)
 
+    # the same with the RMS norm of the fp32 residual ahead of gate / up: this library's norm launch
+    # and the gated pair, against the host framework's norm and element-wise kernels
+    from ishizuki_b200.interface import rmsNorm
+
+    res = dev(synth.activations(rng, 8, 5120).astype(np.float32))
+    nw = dev(np.ones(5120, dtype=np.float16))
+
+    def run_normed_gated():
+        for (gated, _, down), y in zip(mlps, ys):
+            gated(rmsNorm(res, nw, 1e-6), out=h)
+            down(h, out=y)
+
+    def run_normed_stacked():
+        for (_, stacked, down), y in zip(mlps, ys):
+            xn = torch.nn.functional.rms_norm(res, (5120,), nw.float(), 1e-6).half()
+            stacked(xn, out=gu)
+            torch.mul(torch.nn.functional.silu(gu[:, :17408]), gu[:, 17408:], out=h)
+            down(h, out=y)
+
     mb = sum(lin.weightBytes for lin in mlps[0][1:]) / 1e6
     row = {"weight_mb": mb}
-    for name, run in (("gated", run_gated), ("stacked_and_elementwise", run_stacked)):
+    for name, run in (("gated", run_gated), ("stacked_and_elementwise", run_stacked), ("norm_gated", run_normed_gated),
+                      ("norm_stacked_and_elementwise", run_normed_stacked)):
         us = timed_graph(run) / blocks
         row[name] = {"us_per_block": round(us, 2), "gbs": round(mb * 1e3 / us, 1), "frac_of_peak": round(mb * 1e3 / us / peak, 3)}
     table["q4_k_mlp_block_m8"] = row

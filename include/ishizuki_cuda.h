@@ -399,6 +399,18 @@ void ishi_group_destroy(ishi_group *g);
  * with NULL. Lets the error and time-out paths be exercised on a machine without GPUs. */
 ishi_status ishi_group_debug_set_api(const void *table);
 
+/* ---- layer stages around the projections --------------------------------------------------- */
+
+/* The RMS norm ahead of q/k/v and of gate/up (MLXFast.rmsNorm in DecoderLayer.callAsFunction,
+ * Sources/IshizukiKit/Text/TextModel.swift:151-161): y [rows, width] fp16 =
+ * x * rsqrt(mean(x^2) + eps) * weight, fp32 inside. x fp32 (the reference's residual stream) or
+ * fp16; weight [width] fp16, bf16 or fp32; width up to 8192. One launch that joins the stream's
+ * chain of dependent launches (it starts while the launch before it drains, and the product after
+ * it runs its own prologue meanwhile). silu(gate) * up, the other stage of the MLP, is part of
+ * ishi_projection_create_gated. */
+ishi_status ishi_rms_norm(ishi_ctx *ctx, const void *x, int x_dtype, int64_t rows, int64_t width, const void *weight,
+                          int weight_dtype, float eps, void *y, void *stream);
+
 /* ---- EXL3 trellis-coded projections: EXL3Tensor / EXL3Kernels ------------------------------ */
 
 enum { ISHI_EXL3_3INST = 0, ISHI_EXL3_MCG = 1, ISHI_EXL3_MUL1 = 2 };

@@ -54,6 +54,7 @@ SIGNATURES = {
     "ishi_projection_create": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(c_void_p)]),
     "ishi_projection_create_fused": (c_int, [c_void_p, POINTER(WeightDesc), c_int, POINTER(c_void_p)]),
     "ishi_projection_create_gated": (c_int, [c_void_p, POINTER(WeightDesc), POINTER(WeightDesc), POINTER(c_void_p)]),
+    "ishi_rms_norm": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, ctypes.c_float, c_void_p, c_void_p]),
     "ishi_exl3_dequantize": (c_int, [c_void_p, POINTER(EXL3Desc), c_int, c_void_p, c_void_p]),
     "ishi_exl3_rotate": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     "ishi_exl3_matvec": (c_int, [c_void_p, POINTER(EXL3Desc), c_void_p, c_int, c_void_p, c_void_p]),

@@ -1605,6 +1605,21 @@ extern "C" ishi_status ishi_q4k_matmul_few_static(const void *x, int rows, const
   return raised ? ISHI_E_TIMEOUT : ISHI_OK;
 }
 
+ishi_status ishi_rms_norm(ishi_ctx *ctx, const void *x, int x_dtype, int64_t rows, int64_t width, const void *weight,
+                          int weight_dtype, float eps, void *y, void *stream) {
+  if (!ctx) return ISHI_E_INVALID;
+  if (!x || !weight || !y) return fail(ctx, ISHI_E_INVALID, "null pointer");
+  if ((x_dtype != ISHI_DT_F16 && x_dtype != ISHI_DT_F32) || weight_dtype < ISHI_DT_F16 || weight_dtype > ISHI_DT_F32)
+    return fail(ctx, ISHI_E_INVALID, "bad dtype");
+  if (rows < 0 || rows > 65535 || width <= 0 || width > rms_norm_max_width())
+    return fail(ctx, ISHI_E_SHAPE, "rows %lld or width %lld outside this kernel's range (width <= %lld)", (long long)rows,
+                (long long)width, rms_norm_max_width());
+  ISHI_CUDA(ctx, cudaSetDevice(ctx->device));
+  ISHI_CUDA(ctx, launch_rms_norm(x, x_dtype, weight, weight_dtype, rows, width, eps, static_cast<__half *>(y),
+                                 static_cast<cudaStream_t>(stream)));
+  return ISHI_OK;
+}
+
 // ---- EXL3 -----------------------------------------------------------------------------------------
 
 namespace {

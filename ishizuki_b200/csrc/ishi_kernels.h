@@ -47,6 +47,11 @@ cudaError_t launch_ggml_rowdot(int type, const uint8_t *blocks, long long n, lon
                                long long ldy, int transposed, int sm_count, cudaStream_t st);
 cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, cudaStream_t st);
 
+// ---- layer stages around the projections (ishi_stages.cu) -----------------------------------------
+long long rms_norm_max_width();
+cudaError_t launch_rms_norm(const void *x, int x_dtype, const void *w, int w_dtype, long long rows, long long width, float eps,
+                            __half *y, cudaStream_t st);
+
 // ---- EXL3 trellis-coded weights (ishi_exl3.cu) ---------------------------------------------------
 // words16: int16 words per 16 x 16 tile (16 * bits); codebook: 0 3INST, 1 MCG, 2 MUL1; dtypes: 0 fp16, 2 fp32
 bool exl3_rate_supported(int words16, int codebook);

@@ -504,6 +504,18 @@ def hadamardRotate(x: torch.Tensor, block: int, signs: torch.Tensor | None) -> t
     return y.reshape(x.shape)
 
 
+def rmsNorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:  # noqa: N802
+    """MLXFast.rmsNorm(x, weight:, eps:) ahead of a projection (TextModel.swift:151-161): fp32 or
+    fp16 rows in, fp16 out."""
+    ctx = Context.get(x.device.index)
+    h = x.reshape(-1, x.shape[-1]).contiguous()
+    w = weight.contiguous()
+    y = torch.empty(h.shape, dtype=torch.float16, device=x.device)
+    ctx.check(ctx.lib.ishi_rms_norm(ctx.handle, _ptr(h), _OUT_DT[h.dtype], h.shape[0], h.shape[1], _ptr(w), _OUT_DT[w.dtype],
+                                    ctypes.c_float(eps), _ptr(y), _stream()), declined=())
+    return y.reshape(x.shape)
+
+
 class EXL3Tensor:
     """An EXL3 trellis-coded weight (reference: EXL3Tensor, Sources/IshizukiKit/Core/EXL3.swift:9-79):
     ``trellis`` int16 [k / 16, n / 16, 16 * bits], fp16 scale vectors of the input and the output

@@ -125,6 +125,14 @@ def affine_dequantize(w: np.ndarray, scales: np.ndarray, biases: np.ndarray, bit
     return out
 
 
+def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+    """MLXFast.rmsNorm as DecoderLayer uses it (Sources/IshizukiKit/Text/TextModel.swift:151-161):
+    x * rsqrt(mean(x^2) + eps) * weight in fp32, fp16 out. Pinned by the formula only (MLX)."""
+    h = x.astype(np.float32)
+    r = np.float32(1) / np.sqrt((h.astype(np.float64) ** 2).mean(axis=-1, keepdims=True).astype(np.float32) + np.float32(eps))
+    return (h * r * weight.astype(np.float32)).astype(np.float16)
+
+
 def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     """silu(gate) * up on fp16 arrays, the input of the reference's downProj
     (Sources/IshizukiKit/Text/Attention.swift:251: downProj(silu(gateProj(x)) * upProj(x))). Each
