@@ -426,11 +426,12 @@ def format_table(peak: float) -> dict:
             BonsaiRuntime.route = _lib.ROUTE_AUTO
         table[name] = row
         del lins
-    # one of the eight other GGML block types (warp-level kernel through the dense decoder): IQ4_XS
-    lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(GGMLType.iq4Xs), n, k)), GGMLType.iq4Xs, (n, k)))
-            for _ in range(2)]
-    table["iq4_xs_dense_decoder"] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
-    del lins
+    # two of the eight other GGML block types: IQ4_XS has a fragment decoder of its own, IQ3_S runs on
+    # the warp-level kernel through the dense decoder
+    for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s_dense_decoder", GGMLType.iq3S)):
+        lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k))) for _ in range(2)]
+        table[name] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
+        del lins
     torch.cuda.empty_cache()
     # configuration 1: a single 4096 x 4096 affine 4-bit group-64 projection (32 distinct weights)
     lins = [make("affine4_g64", 4096, 4096) for _ in range(32)]

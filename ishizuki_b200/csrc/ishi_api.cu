@@ -25,6 +25,7 @@ namespace ishi {
 const FragOps *frag_ops_q4k();
 const FragOps *frag_ops_q6k();
 const FragOps *frag_ops_iq2xs();
+const FragOps *frag_ops_iq4xs();
 const FragOps *frag_ops_ggml_a(int type);
 const FragOps *frag_ops_ggml_b(int type);
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
@@ -401,6 +402,7 @@ const FragOps *frag_ops_for(const ishi_weight_desc &d) {
     if (d.ggml_type == ISHI_GGML_Q4_K) return frag_ops_q4k();
     if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
     if (d.ggml_type == ISHI_GGML_IQ2_XS) return frag_ops_iq2xs();
+    if (d.ggml_type == ISHI_GGML_IQ4_XS) return frag_ops_iq4xs();
     if (const FragOps *ops = frag_ops_ggml_a(d.ggml_type)) return ops;
     return frag_ops_ggml_b(d.ggml_type);  // the other block types, through the dense decoder
   }
@@ -677,10 +679,12 @@ ishi_status ggml_raw(ishi_ctx *ctx, const void *x, int rows, const void *blocks,
   return raw_product(ctx, d, x, rows, y, gemv, static_cast<cudaStream_t>(stream));
 }
 
-// The warp-level kernel rotates x while it stages it when a block fits one 256-wide unit.
+// The warp-level kernel rotates x while it stages it when a block fits one 256-wide unit: the
+// staging of the affine packs does (the reference's rotated packs are affine, Hadamard.swift:51-86);
+// the GGUF decoders' staging does not, their input is rotated by the stand-alone kernel first.
 bool rotates_in_kernel(const ishi_projection *p) {
   const int b = p->d.hadamard_block;
-  return p->frag.ok && b >= 8 && b <= 256 && (b & (b - 1)) == 0;
+  return p->frag.ok && p->d.kind == ISHI_KIND_AFFINE && b >= 8 && b <= 256 && (b & (b - 1)) == 0;
 }
 
 // rotate: x is unrotated and the projection's rotation is applied inside the product kernel

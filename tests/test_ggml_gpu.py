@@ -304,6 +304,22 @@ def test_a_projection_under_another_ones_plan_gives_the_same_bits():
         b.set_plan((2, 25, 8, 3))  # more warps than a block holds: not a plan of this projection
 
 
+@pytest.mark.parametrize("type_id", [GGMLType.q4K, GGMLType.q6K])
+def test_rotated_input_ahead_of_a_gguf_projection(type_id):
+    """A GGUF projection with a rotation block: the input goes through the stand-alone rotation
+    kernel first (the GGUF decoders' staging does not rotate), the product is that of the rotated
+    rows."""
+    rng = np.random.default_rng(int(type_id))
+    n, k = 96, 1024
+    blocks = synth.ggml_blocks(rng, int(type_id), n, k)
+    lin = PackedLinear(None, None, None, None, 128, ggml=GGUFBlocks(dev(blocks), type_id, (n, k)))
+    for m in (1, 8):
+        x = synth.activations(rng, m, k)
+        want32, _ = oracle.ggml_matmul(int(type_id), blocks, oracle.hadamard_rotate(x, 128), n)
+        assert rel_err(lin(dev(x)).cpu().numpy(), want32) < TOL
+    lin.ctx.poll()
+
+
 def _check_gated(gated, stacked, x, want_gate, want_up):
     """The gated launch against (a) the oracle's silu(gate) * up on the oracle's fp16 products and
     (b) the same formula on this library's own stacked products, which differ from the kernel's
