@@ -62,6 +62,26 @@ def test_decode_and_product_on_random_trellises(words, codebook):
     assert EXL3Kernels.matvec(dev(rng.standard_normal((9, k)).astype(np.float16)), t) is None
 
 
+@pytest.mark.parametrize("n", [8192, 17408])
+def test_product_with_several_tile_columns_per_block(n):
+    """Wide outputs: a thread block takes two or four adjacent tile columns. Checked against the
+    expanded weight (whose decode the tests above hold to the oracle bit for bit)."""
+    rng = np.random.default_rng(n)
+    k = 512
+    for words, codebook in ((64, EXL3Tensor.mul1), (48, EXL3Tensor.threeInst)):
+        trellis = random_trellis(rng, k, n, words)
+        t = EXL3Tensor(dev(trellis), None, None, codebook)
+        w = EXL3Kernels.dequantize(t, torch.float32).double()
+        sample = oracle.exl3_dequantize(trellis[:, :16], codebook)  # the first 256 columns against the oracle
+        assert np.array_equal(w[:, :256].float().cpu().numpy().view(np.uint32), sample.view(np.uint32))
+        for m in (1, 8):
+            x = dev(rng.standard_normal((m, k)).astype(np.float16))
+            y = EXL3Kernels.matvec(x, t).double()
+            want = x.double() @ w
+            bound = (x.double().abs() @ w.abs()).max()
+            assert float((y - want).abs().max() / bound) < 1e-5
+
+
 def test_rotation_matches_the_oracle():
     # EXL3Tests.rotationMatchesHadamard
     rng = np.random.default_rng(5)
