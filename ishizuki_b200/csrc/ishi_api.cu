@@ -26,6 +26,8 @@ const FragOps *frag_ops_q4k();
 const FragOps *frag_ops_q6k();
 const FragOps *frag_ops_iq2xs();
 const FragOps *frag_ops_iq4xs();
+const FragOps *frag_ops_iq2xxs();
+const FragOps *frag_ops_iq2s();
 const FragOps *frag_ops_ggml_a(int type);
 const FragOps *frag_ops_ggml_b(int type);
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
@@ -403,6 +405,8 @@ const FragOps *frag_ops_for(const ishi_weight_desc &d) {
     if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
     if (d.ggml_type == ISHI_GGML_IQ2_XS) return frag_ops_iq2xs();
     if (d.ggml_type == ISHI_GGML_IQ4_XS) return frag_ops_iq4xs();
+    if (d.ggml_type == ISHI_GGML_IQ2_XXS) return frag_ops_iq2xxs();
+    if (d.ggml_type == ISHI_GGML_IQ2_S) return frag_ops_iq2s();
     if (const FragOps *ops = frag_ops_ggml_a(d.ggml_type)) return ops;
     return frag_ops_ggml_b(d.ggml_type);  // the other block types, through the dense decoder
   }
