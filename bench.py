@@ -426,9 +426,10 @@ def format_table(peak: float) -> dict:
             BonsaiRuntime.route = _lib.ROUTE_AUTO
         table[name] = row
         del lins
-    # three of the eight other GGML block types: IQ4_XS and IQ3_S have fragment decoders of their
-    # own, Q2_K runs on the warp-level kernel through the dense decoder
-    for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s", GGMLType.iq3S), ("q2_k_dense_decoder", GGMLType.q2K)):
+    # four of the eight other GGML block types: IQ4_XS, IQ3_S and Q2_K have fragment decoders of
+    # their own, IQ1_S runs on the warp-level kernel through the dense decoder
+    for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s", GGMLType.iq3S), ("q2_k", GGMLType.q2K),
+                          ("iq1_s_dense_decoder", GGMLType.iq1S)):
         lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k))) for _ in range(2)]
         table[name] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
         del lins

@@ -1,4 +1,4 @@
-// The GGML block types without a fragment decoder of their own (Q2_K, IQ1_S, IQ1_M;
+// The GGML block types without a fragment decoder of their own (IQ1_S, IQ1_M;
 // any of the eight other types can run here) on the warp-level kernel, through the dense decoder: no bit tricks here, a lane decodes the
 // sixteen weights of a sub-block with decode8 (ggml_decode.cuh, the same code that defines the
 // decoded weight values) and rounds them to fp16 pairs for the MMA. Reference: the block bodies at

@@ -30,6 +30,7 @@ const FragOps *frag_ops_iq2xxs();
 const FragOps *frag_ops_iq2s();
 const FragOps *frag_ops_iq3xxs();
 const FragOps *frag_ops_iq3s();
+const FragOps *frag_ops_q2k();
 const FragOps *frag_ops_ggml_a(int type);
 const FragOps *frag_ops_ggml_b(int type);
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
@@ -411,6 +412,7 @@ const FragOps *frag_ops_for(const ishi_weight_desc &d) {
     if (d.ggml_type == ISHI_GGML_IQ2_S) return frag_ops_iq2s();
     if (d.ggml_type == ISHI_GGML_IQ3_XXS) return frag_ops_iq3xxs();
     if (d.ggml_type == ISHI_GGML_IQ3_S) return frag_ops_iq3s();
+    if (d.ggml_type == ISHI_GGML_Q2_K) return frag_ops_q2k();
     if (const FragOps *ops = frag_ops_ggml_a(d.ggml_type)) return ops;
     return frag_ops_ggml_b(d.ggml_type);  // the other block types, through the dense decoder
   }
