@@ -10,8 +10,8 @@ fp16 outputs. Projections that read the same input are stacked into one launch (
 a layer is four launches; every projection has its own weights (12.27 GB per pass, far more than
 L2) and its own fresh N(0,1) activations. `--workload mlp` runs gate/up/down only (the 1-GPU MLP
 configuration), `--workload formats` only the per-format side table (every weight format on the
-gate shape at M = 1 and M = 8, the 4096 x 4096 affine projection, a ternary layer; ISHI_BENCH_FORMATS
-and ISHI_BENCH_ROWS narrow it for profiler captures). Inputs are synthetic with the configured value distributions, drawn on the GPU
+gate shape at M = 1 and M = 8, the 4096 x 4096 affine projection, a ternary layer, an MLP block with
+its stages, EXL3; ISHI_BENCH_FORMATS and ISHI_BENCH_ROWS narrow it for profiler captures). Inputs are synthetic with the configured value distributions, drawn on the GPU
 from seeded generators: real GGUF files are not available where this runs.
 
 The metric is weight GB/s: compressed weight bytes streamed per second (GB = 1e9), the
