@@ -426,11 +426,16 @@ def format_table(peak: float) -> dict:
             BonsaiRuntime.route = _lib.ROUTE_AUTO
         table[name] = row
         del lins
-    # four of the eight other GGML block types: IQ4_XS, IQ3_S and Q2_K have fragment decoders of
-    # their own, IQ1_S runs on the warp-level kernel through the dense decoder
-    for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s", GGMLType.iq3S), ("q2_k", GGMLType.q2K),
-                          ("iq1_s_dense_decoder", GGMLType.iq1S)):
-        lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k))) for _ in range(2)]
+    # four of the eight other GGML block types on their own fragment decoders, and one of them
+    # through the dense decoder (ISHI_DENSE_DECODER at projection create), the path they ran on before
+    for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s", GGMLType.iq3S), ("q2_k", GGMLType.q2K), ("iq1_s", GGMLType.iq1S),
+                          ("iq3_s_dense_decoder", GGMLType.iq3S)):
+        if name.endswith("_dense_decoder"):
+            os.environ["ISHI_DENSE_DECODER"] = "1"
+        try:
+            lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k))) for _ in range(2)]
+        finally:
+            os.environ.pop("ISHI_DENSE_DECODER", None)
         table[name] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
         del lins
     torch.cuda.empty_cache()

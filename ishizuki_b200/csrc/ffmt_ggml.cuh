@@ -1,5 +1,6 @@
-// The GGML block types without a fragment decoder of their own (IQ1_S, IQ1_M;
-// any of the eight other types can run here) on the warp-level kernel, through the dense decoder: no bit tricks here, a lane decodes the
+// The eight other GGML block types (Q2_K, IQ2_XXS, IQ2_S, IQ3_XXS, IQ3_S, IQ1_S, IQ1_M, IQ4_XS) on the
+// warp-level kernel through the dense decoder, the comparison path beside their own fragment
+// decoders (ISHI_DENSE_DECODER=1 at projection create): no bit tricks here, a lane decodes the
 // sixteen weights of a sub-block with decode8 (ggml_decode.cuh, the same code that defines the
 // decoded weight values) and rounds them to fp16 pairs for the MMA. Reference: the block bodies at
 // Sources/IshizukiKit/Core/GGMLKernels.swift:568-582,630-761 and GGMLDequant.swift:125-150,222-428.

@@ -31,6 +31,8 @@ const FragOps *frag_ops_iq2s();
 const FragOps *frag_ops_iq3xxs();
 const FragOps *frag_ops_iq3s();
 const FragOps *frag_ops_q2k();
+const FragOps *frag_ops_iq1s();
+const FragOps *frag_ops_iq1m();
 const FragOps *frag_ops_ggml_a(int type);
 const FragOps *frag_ops_ggml_b(int type);
 const FragOps *frag_ops_affine4(int group_size, bool bf16);
@@ -407,12 +409,18 @@ const FragOps *frag_ops_for(const ishi_weight_desc &d) {
     if (d.ggml_type == ISHI_GGML_Q4_K) return frag_ops_q4k();
     if (d.ggml_type == ISHI_GGML_Q6_K) return frag_ops_q6k();
     if (d.ggml_type == ISHI_GGML_IQ2_XS) return frag_ops_iq2xs();
-    if (d.ggml_type == ISHI_GGML_IQ4_XS) return frag_ops_iq4xs();
-    if (d.ggml_type == ISHI_GGML_IQ2_XXS) return frag_ops_iq2xxs();
-    if (d.ggml_type == ISHI_GGML_IQ2_S) return frag_ops_iq2s();
-    if (d.ggml_type == ISHI_GGML_IQ3_XXS) return frag_ops_iq3xxs();
-    if (d.ggml_type == ISHI_GGML_IQ3_S) return frag_ops_iq3s();
-    if (d.ggml_type == ISHI_GGML_Q2_K) return frag_ops_q2k();
+    // ISHI_DENSE_DECODER=1: the eight other types through the dense decoder instead of their own
+    // fragment decoders (to compare the two, and to keep that path exercised)
+    if (!getenv("ISHI_DENSE_DECODER")) {
+      if (d.ggml_type == ISHI_GGML_IQ4_XS) return frag_ops_iq4xs();
+      if (d.ggml_type == ISHI_GGML_IQ2_XXS) return frag_ops_iq2xxs();
+      if (d.ggml_type == ISHI_GGML_IQ2_S) return frag_ops_iq2s();
+      if (d.ggml_type == ISHI_GGML_IQ3_XXS) return frag_ops_iq3xxs();
+      if (d.ggml_type == ISHI_GGML_IQ3_S) return frag_ops_iq3s();
+      if (d.ggml_type == ISHI_GGML_Q2_K) return frag_ops_q2k();
+      if (d.ggml_type == ISHI_GGML_IQ1_S) return frag_ops_iq1s();
+      if (d.ggml_type == ISHI_GGML_IQ1_M) return frag_ops_iq1m();
+    }
     if (const FragOps *ops = frag_ops_ggml_a(d.ggml_type)) return ops;
     return frag_ops_ggml_b(d.ggml_type);  // the other block types, through the dense decoder
   }

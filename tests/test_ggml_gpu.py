@@ -320,6 +320,25 @@ def test_rotated_input_ahead_of_a_gguf_projection(type_id):
     lin.ctx.poll()
 
 
+@pytest.mark.parametrize("type_id", [GGMLType.q2K, GGMLType.iq2S, GGMLType.iq3Xxs, GGMLType.iq4Xs, GGMLType.iq1M])
+def test_the_dense_decoder_path_of_the_other_block_types(type_id, monkeypatch):
+    """ISHI_DENSE_DECODER=1 at create sends the eight other block types through the dense decoder
+    (decode8 into fp16 fragments) instead of their own fragment decoders: the same products."""
+    rng = np.random.default_rng(int(type_id) + 500)
+    n, k = 200, 1024
+    blocks = synth.ggml_blocks(rng, int(type_id), n, k)
+    own = PackedLinear(ggml=GGUFBlocks(dev(blocks), type_id, (n, k)))
+    monkeypatch.setenv("ISHI_DENSE_DECODER", "1")
+    dense = PackedLinear(ggml=GGUFBlocks(dev(blocks), type_id, (n, k)))
+    monkeypatch.delenv("ISHI_DENSE_DECODER")
+    for m in (1, 8):
+        x = synth.activations(rng, m, k)
+        want32, _ = oracle.ggml_matmul(int(type_id), blocks, x, n)
+        assert rel_err(own(dev(x)).cpu().numpy(), want32) < TOL
+        assert rel_err(dense(dev(x)).cpu().numpy(), want32) < TOL
+    own.ctx.poll()
+
+
 def _check_gated(gated, stacked, x, want_gate, want_up):
     """The gated launch against (a) the oracle's silu(gate) * up on the oracle's fp16 products and
     (b) the same formula on this library's own stacked products, which differ from the kernel's
