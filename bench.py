@@ -363,6 +363,26 @@ def format_table(peak: float) -> dict:
     # ISHI_BENCH_FORMATS=name[,name]: only these rows of the first group (profiler captures of one format)
     only = [f for f in os.environ.get("ISHI_BENCH_FORMATS", "").split(",") if f]
     row_counts = [int(r) for r in os.environ.get("ISHI_BENCH_ROWS", "1,8").split(",")]  # activation rows M
+    def other_rows():
+        # four of the eight other GGML block types on their own fragment decoders, and one of them
+        # through the dense decoder (ISHI_DENSE_DECODER at projection create), the path they ran on before
+        for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s", GGMLType.iq3S), ("q2_k", GGMLType.q2K), ("iq1_s", GGMLType.iq1S),
+                              ("iq3_s_dense_decoder", GGMLType.iq3S)):
+            if only and name not in only:
+                continue
+            if name.endswith("_dense_decoder"):
+                os.environ["ISHI_DENSE_DECODER"] = "1"
+            try:
+                lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k)))
+                        for _ in range(2)]
+            finally:
+                os.environ.pop("ISHI_DENSE_DECODER", None)
+            table[name] = {"weight_mb": lins[0].weightBytes / 1e6}
+            for m in row_counts:
+                table[name]["m%d" % m] = measure(lins, m, k)
+            del lins
+        torch.cuda.empty_cache()
+
     def exl3_rows():
         # EXL3 trellis-coded weights on the gate shape, 4 bits, the product kernel alone (no rotations)
         from ishizuki_b200.interface import EXL3Kernels, EXL3Tensor
@@ -413,6 +433,7 @@ def format_table(peak: float) -> dict:
         del lins
         torch.cuda.empty_cache()
     if only:
+        other_rows()
         exl3_rows()
         return table
     # one row on CUDA cores beside the tensor-core kernel on the smallest and the tallest projection
@@ -426,19 +447,7 @@ def format_table(peak: float) -> dict:
             BonsaiRuntime.route = _lib.ROUTE_AUTO
         table[name] = row
         del lins
-    # four of the eight other GGML block types on their own fragment decoders, and one of them
-    # through the dense decoder (ISHI_DENSE_DECODER at projection create), the path they ran on before
-    for name, type_id in (("iq4_xs", GGMLType.iq4Xs), ("iq3_s", GGMLType.iq3S), ("q2_k", GGMLType.q2K), ("iq1_s", GGMLType.iq1S),
-                          ("iq3_s_dense_decoder", GGMLType.iq3S)):
-        if name.endswith("_dense_decoder"):
-            os.environ["ISHI_DENSE_DECODER"] = "1"
-        try:
-            lins = [PackedLinear(ggml=GGUFBlocks(dev(synth.ggml_blocks(rng, int(type_id), n, k)), type_id, (n, k))) for _ in range(2)]
-        finally:
-            os.environ.pop("ISHI_DENSE_DECODER", None)
-        table[name] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, k), "m8": measure(lins, 8, k)}
-        del lins
-    torch.cuda.empty_cache()
+    other_rows()
     # configuration 1: a single 4096 x 4096 affine 4-bit group-64 projection (32 distinct weights)
     lins = [make("affine4_g64", 4096, 4096) for _ in range(32)]
     table["affine4_g64_4096x4096"] = {"weight_mb": lins[0].weightBytes / 1e6, "m1": measure(lins, 1, 4096),
