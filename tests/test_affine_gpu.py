@@ -115,6 +115,16 @@ def test_ternary_rotated_projection(n, k):
         assert np.array_equal(xr_dev.cpu().numpy().view(np.uint16), xr.view(np.uint16))
         two = lin.applyRotated(xr_dev).cpu().numpy().astype(np.float32)
         assert rel_err(two, y.cpu().numpy().astype(np.float32)) < 5e-4
+        if rows == 1:
+            # the same staging feeds the single-row CUDA-core route
+            from ishizuki_b200 import _lib
+            from ishizuki_b200.interface import BonsaiRuntime
+
+            BonsaiRuntime.route = _lib.ROUTE_GEMV
+            try:
+                assert rel_err(lin(dev(x)).cpu().numpy(), want32) < TOL
+            finally:
+                BonsaiRuntime.route = _lib.ROUTE_AUTO
     lin.ctx.poll()
 
 
