@@ -48,8 +48,9 @@ enum {
 
 /* GGML block types, numbered as in GGUF (Sources/IshizukiKit/Config/GGUFFile.swift:13-44): the
  * eleven quantized types the reference reads (GGMLDequant.supported,
- * Sources/IshizukiKit/Core/GGMLDequant.swift:19-24). Q4_K, Q6_K and IQ2_XS have streaming product
- * kernels; the others are decoded bit-exactly and multiplied by a one-warp-per-row kernel. */
+ * Sources/IshizukiKit/Core/GGMLDequant.swift:19-24). Every one of them has a fragment decoder on
+ * the warp-level product kernel (the weight is decoded inside the multiply, never expanded in
+ * memory); a one-warp-per-row kernel on the plain blocks is the fallback for inputs too wide for it. */
 enum {
   ISHI_GGML_Q2_K = 10, ISHI_GGML_Q4_K = 12, ISHI_GGML_Q6_K = 14, ISHI_GGML_IQ2_XXS = 16, ISHI_GGML_IQ2_XS = 17,
   ISHI_GGML_IQ3_XXS = 18, ISHI_GGML_IQ1_S = 19, ISHI_GGML_IQ3_S = 21, ISHI_GGML_IQ2_S = 22, ISHI_GGML_IQ4_XS = 23,
@@ -120,8 +121,8 @@ ishi_status ishi_projection_create(ishi_ctx *ctx, const ishi_weight_desc *desc,
  * read the same input (the reference's q/k/v, Sources/IshizukiKit/Text/Attention.swift:75-83, and
  * gate/up, Attention.swift:251, which it runs as separate kernels): one launch streams all of them,
  * so the per-launch costs are paid once. count in 1...4; all descriptors must agree in kind, type,
- * width, group size, scale dtype, k and rotation. GGUF Q4_K and the 4-/2-bit affine packs only
- * (ISHI_E_UNSUPPORTED otherwise). */
+ * width, group size, scale dtype, k and rotation. Every GGUF block type and the 4-/2-bit affine
+ * packs with fp16 / bf16 scales: the formats of the warp-level kernel (ISHI_E_UNSUPPORTED otherwise). */
 ishi_status ishi_projection_create_fused(ishi_ctx *ctx, const ishi_weight_desc *descs, int count,
                                          ishi_projection **out);
 /* The MLP's gate and up projections as ONE projection whose output is the input of downProj:
