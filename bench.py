@@ -536,6 +536,27 @@ def format_table(peak: float) -> dict:
     torch.cuda.empty_cache()
     exl3_rows()
     torch.cuda.empty_cache()
+    # the LM head of the verify step (248320 x 5120, Q4_K) with the arg-max of every drafted row:
+    # ishi_projection_apply_argmax = the product into the projection's own logits buffer and the
+    # arg-max kernel; two heads alternate so that the weights come from HBM
+    heads = [PackedLinear(ggml=GGUFBlocks(q4k_blocks_device(4242 + i, 248320, 5120), GGMLType.q4K, (248320, 5120)))
+             for i in range(2)]
+    row = {"weight_mb": heads[0].weightBytes / 1e6}
+    for m in (1, 8):
+        x = dev(synth.activations(rng, m, 5120))
+        heads[0].argmax(x)  # the first call allocates the logits buffer, outside the capture
+        heads[1].argmax(x)
+
+        def run():
+            for head in heads:
+                head.argmax(x)
+
+        us = timed_graph(run, reps=10) / len(heads)
+        gbs = row["weight_mb"] * 1e3 / us
+        row["m%d" % m] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+    table["lm_head_q4_k_248320x5120_argmax"] = row
+    del heads
+    torch.cuda.empty_cache()
     return table
 
 

@@ -112,52 +112,82 @@ __global__ void __launch_bounds__(256) ggml_rowdot_kernel(const uint8_t *__restr
 
 // Index of the largest of n fp16 logits per row, the lowest index among equals (MLX argMax as the
 // greedy verify uses it, Sources/IshizukiKit/Generate/SpeculativeGeneration.swift:173-177). NaN
-// never wins. One CTA per row.
-__global__ void __launch_bounds__(1024) argmax_rows_kernel(const __half *__restrict__ y, long long n, long long ldy,
-                                                           int *__restrict__ out) {
-  __shared__ float s_val[32];
-  __shared__ long long s_idx[32];
-  const __half *row = y + (long long)blockIdx.x * ldy;
+// never wins. A row is cut into chunks, one CTA each (grid: chunks x rows): 16-byte loads where the
+// row allows, the chunk's best (value, index) goes to `parts`, and the CTA that counts itself last
+// for its row reduces the row's parts. Value first, then the lower index: the result does not
+// depend on the order in which the CTAs finish. `counters` (one per row) are zero between launches.
+struct ArgPart {
+  float v;
+  int i;
+};
+__device__ __forceinline__ bool arg_better(float v, int i, float bv, int bi) {
+  return i >= 0 && (bi < 0 || v > bv || (v == bv && i < bi));
+}
+__device__ __forceinline__ void arg_take(float v, int i, float &best, int &at) {
+  if (v > best || (at < 0 && v == best)) best = v, at = i;  // indices come in ascending order per thread
+}
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const __half *__restrict__ y, long long n, long long ldy, int chunk,
+                                                          ArgPart *__restrict__ parts, unsigned *__restrict__ counters,
+                                                          int *__restrict__ out) {
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  __shared__ bool s_last;
+  const int r = blockIdx.y, c = blockIdx.x, nchunks = gridDim.x;
+  const __half *row = y + (long long)r * ldy;
+  const long long lo = (long long)c * chunk, hi = lo + chunk < n ? lo + chunk : n;
   float best = -INFINITY;
-  long long at = -1;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = __half2float(row[i]);
-    if (v > best || (at < 0 && v == best)) {
-      best = v;
-      at = i;
+  int at = -1;
+  long long i = lo + (long long)threadIdx.x * 8;
+  if ((reinterpret_cast<uintptr_t>(row + lo) & 15u) == 0) {
+    for (; i + 8 <= hi; i += 256 * 8) {
+      const uint4 q = *reinterpret_cast<const uint4 *>(row + i);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e]));
+        arg_take(f.x, (int)i + 2 * e, best, at);
+        arg_take(f.y, (int)i + 2 * e + 1, best, at);
+      }
     }
   }
-  auto better = [](float v, long long i, float bv, long long bi) {
-    return i >= 0 && (bi < 0 || v > bv || (v == bv && i < bi));
-  };
+  // what the 16-byte loads left: a misaligned chunk, the last few values
+  for (; i < hi; i += 256 * 8)
+    for (long long k = i; k < hi && k < i + 8; ++k) arg_take(__half2float(row[k]), (int)k, best, at);
 #pragma unroll
   for (int d = 16; d >= 1; d >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, d);
-    const long long oi = __shfl_xor_sync(0xffffffffu, at, d);
-    if (better(ov, oi, best, at)) {
-      best = ov;
-      at = oi;
-    }
+    const int oi = __shfl_xor_sync(0xffffffffu, at, d);
+    if (arg_better(ov, oi, best, at)) best = ov, at = oi;
   }
-  if ((threadIdx.x & 31) == 0) {
-    s_val[threadIdx.x >> 5] = best;
-    s_idx[threadIdx.x >> 5] = at;
+  if ((threadIdx.x & 31) == 0) s_val[threadIdx.x >> 5] = best, s_idx[threadIdx.x >> 5] = at;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (arg_better(s_val[w], s_idx[w], best, at)) best = s_val[w], at = s_idx[w];
+    parts[(long long)r * nchunks + c] = ArgPart{best, at};
+    __threadfence();
+    const unsigned before = atomicAdd(counters + r, 1u);
+    s_last = before == (unsigned)nchunks - 1;
   }
   __syncthreads();
-  if (threadIdx.x < 32) {
-    const int nw = (blockDim.x + 31) >> 5;
-    best = threadIdx.x < nw ? s_val[threadIdx.x] : -INFINITY;
-    at = threadIdx.x < nw ? s_idx[threadIdx.x] : -1;
+  if (!s_last || threadIdx.x >= 32) return;
+  __threadfence();
+  best = -INFINITY, at = -1;
+  for (int k = threadIdx.x; k < nchunks; k += 32) {
+    const ArgPart *pt = parts + (long long)r * nchunks + k;
+    const float pv = __ldcg(&pt->v);  // written by other CTAs of this launch: from L2
+    const int pi = __ldcg(&pt->i);
+    if (arg_better(pv, pi, best, at)) best = pv, at = pi;
+  }
 #pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, d);
-      const long long oi = __shfl_xor_sync(0xffffffffu, at, d);
-      if (better(ov, oi, best, at)) {
-        best = ov;
-        at = oi;
-      }
-    }
-    if (threadIdx.x == 0) out[blockIdx.x] = (int)(at < 0 ? 0 : at);
+  for (int d = 16; d >= 1; d >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+    const int oi = __shfl_xor_sync(0xffffffffu, at, d);
+    if (arg_better(ov, oi, best, at)) best = ov, at = oi;
+  }
+  if (threadIdx.x == 0) {
+    out[r] = at < 0 ? 0 : at;
+    counters[r] = 0;  // for the next launch on this stream
   }
 }
 
@@ -225,8 +255,17 @@ cudaError_t launch_ggml_rowdot(int type, const uint8_t *blocks, long long n, lon
   });
 }
 
-cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, cudaStream_t st) {
-  argmax_rows_kernel<<<rows, 1024, 0, st>>>(y, n, ldy, out);
+// scratch: ishi::argmax_scratch_bytes() bytes, zero before the first launch
+size_t argmax_scratch_bytes() { return (size_t)16 * 1024 * sizeof(ArgPart) + 16 * sizeof(unsigned); }
+
+cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, void *scratch, cudaStream_t st) {
+  if (rows < 1 || rows > 16 || n < 1 || n > 0x7fffffffll) return cudaErrorInvalidValue;
+  long long chunk = 8192;
+  while ((n + chunk - 1) / chunk > 1024) chunk *= 2;
+  const int nchunks = (int)((n + chunk - 1) / chunk);
+  ArgPart *parts = static_cast<ArgPart *>(scratch);
+  unsigned *counters = reinterpret_cast<unsigned *>(parts + 16 * 1024);
+  argmax_rows_kernel<<<dim3(nchunks, rows), 256, 0, st>>>(y, n, ldy, (int)chunk, parts, counters, out);
   return cudaGetLastError();
 }
 

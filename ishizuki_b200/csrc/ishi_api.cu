@@ -1200,14 +1200,22 @@ ishi_status ishi_projection_apply_argmax(ishi_projection *p, const void *x, int 
     // the first call allocates the projection's logits buffer (make it outside stream capture)
     std::lock_guard<std::mutex> g(ctx->lock);
     if (!p->logits) {
+      // [16][n] logits, then the arg-max kernel's scratch (its counters start at zero)
       __half *l = nullptr;
-      if (cudaMalloc(&l, (size_t)16 * out_rows(p) * sizeof(__half)) != cudaSuccess) return fail(ctx, ISHI_E_NOMEM, "logits buffer");
+      const size_t logits_bytes = ((size_t)16 * out_rows(p) * sizeof(__half) + 255) & ~(size_t)255;
+      if (cudaMalloc(&l, logits_bytes + argmax_scratch_bytes()) != cudaSuccess) return fail(ctx, ISHI_E_NOMEM, "logits buffer");
+      if (cudaMemset(reinterpret_cast<uint8_t *>(l) + logits_bytes, 0, argmax_scratch_bytes()) != cudaSuccess) {
+        cudaFree(l);
+        return fail(ctx, ISHI_E_CUDA, "clearing the arg-max scratch failed");
+      }
       p->logits = l;
     }
   }
   ishi_status s = ishi_projection_apply(p, x, rows, p->logits, out_rows(p), 0, stream);
   if (s != ISHI_OK) return s;
-  ISHI_CUDA(ctx, launch_argmax_rows(p->logits, rows, out_rows(p), out_rows(p), argmax_dev, static_cast<cudaStream_t>(stream)));
+  const size_t logits_bytes = ((size_t)16 * out_rows(p) * sizeof(__half) + 255) & ~(size_t)255;
+  ISHI_CUDA(ctx, launch_argmax_rows(p->logits, rows, out_rows(p), out_rows(p), argmax_dev,
+                                    reinterpret_cast<uint8_t *>(p->logits) + logits_bytes, static_cast<cudaStream_t>(stream)));
   return ISHI_OK;
 }
 

@@ -45,7 +45,8 @@ cudaError_t launch_ggml_gather(int type, const int *ids, long long count, const 
                                long long k, void *out, int out_dtype, int sm_count, cudaStream_t st);
 cudaError_t launch_ggml_rowdot(int type, const uint8_t *blocks, long long n, long long k, const __half *x, int rows, __half *y,
                                long long ldy, int transposed, int sm_count, cudaStream_t st);
-cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, cudaStream_t st);
+size_t argmax_scratch_bytes();  // zeroed once; launch_argmax_rows leaves it zeroed
+cudaError_t launch_argmax_rows(const __half *y, int rows, long long n, long long ldy, int *out, void *scratch, cudaStream_t st);
 
 // ---- layer stages around the projections (ishi_stages.cu) -----------------------------------------
 long long rms_norm_max_width();

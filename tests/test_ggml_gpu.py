@@ -469,6 +469,20 @@ def test_head_argmax_matches_argmax_of_the_logits(type_id, m):
     assert np.all(want32[np.arange(m), got] >= top - 2e-3 * np.abs(want32).max())
 
 
+def test_head_argmax_on_rows_that_are_not_16_byte_aligned():
+    """n not a multiple of 8: every logits row but the first starts off the 16-byte grid and is read
+    value by value; repeated calls reuse the kernel's counters."""
+    rng = np.random.default_rng(31)
+    n, k = 9004, 256
+    blocks = synth.q4k_blocks(rng, n, k)
+    lin = PackedLinear(ggml=GGUFBlocks(dev(blocks), GGMLType.q4K, (n, k)))
+    for m in (3, 16, 1):
+        x = synth.activations(rng, m, k)
+        logits = lin(dev(x)).float().cpu().numpy()
+        for _ in range(2):
+            assert np.array_equal(lin.argmax(dev(x)).cpu().numpy(), logits.argmax(axis=1))
+
+
 def test_argmax_ties_take_the_lowest_index():
     n, k = 4096, 256
     blocks = np.zeros((n, 144), dtype=np.uint8)  # every weight decodes to zero: all logits equal
